@@ -399,6 +399,13 @@ typedef struct b200_latent_prefill_args {
   int n_seqs, max_q_len, n_head, dk, dv;
   float scale;
   int dtype;
+  /* optional (zero / NULL: absent).  k2: a key part of dk2 numbers per position shared by all heads, met by the LAST dk2 numbers
+   * of each query head (dk counts the whole query head; k then holds dk - dk2 numbers per head).  sink: one logit per head (model
+   * dtype) that joins the softmax denominator only.  gate: rows of ldg numbers; the output is multiplied by sigmoid(gate[row, h])
+   * (gate_mode 1) or sigmoid(gate[row, h * dv + c]) (gate_mode 2). */
+  const void* k2; int64_t ldk2; int dk2;
+  const void* sink;
+  const void* gate; int64_t ldg; int gate_mode;
 } b200_latent_prefill_args;
 int b200_latent_prefill(const b200_latent_prefill_args* args, b200_stream_t stream);
 /* The same attention on the tensor cores for bf16 operands with dk = dv = head_size in {64, 128} (the kernel of b200_attn_prefill
@@ -416,6 +423,11 @@ typedef struct b200_latent_decode_args {
   float scale;
   int dtype;
   void* workspace; size_t workspace_bytes;
+  /* optional (zero / NULL: absent), as in b200_latent_prefill_args.  With dk2 > 0 a query head is [dk | dk2] numbers and a cache row
+   * [r latent | dk2 shared key part]: slot_stride and the workspace count r + dk2 numbers per row. */
+  int dk2;
+  const void* sink;
+  const void* gate; int64_t ldg; int gate_mode;
 } b200_latent_decode_args;
 size_t b200_latent_decode_workspace_bytes(int batch, int n_head, int r, int n_split);
 int b200_latent_decode(const b200_latent_decode_args* args, b200_stream_t stream);
@@ -535,6 +547,49 @@ int b200_window_attn_tune(int force_tiled_kernel);
 /* the step's rows among each sequence's last `ring` positions go to their ring rows (call after b200_window_attn) */
 int b200_ring_store(const void* k, int64_t ldk, const void* v, int64_t ldv, void* k_ring, void* v_ring, int ring, int kcols, int vcols,
                     const int32_t* seqs, const int32_t* row_seq, int64_t rows, int dtype, b200_stream_t stream);
+
+
+/* ---- grouped norms with an average over depth, per-head rotation, attention whose scores mix over the heads ------------------ */
+/* x_out = x_in + gnorm(y) * post_w (fp32; y NULL: x_out = x_in); avg = sum_{j < m} depth_w[j] X_j with X_j = stack + j * stack_stride
+ * for j < m - 1 and X_{m-1} = x_out (avg NULL: skipped); act = dtype(gnorm(avg or x_out) * pre_w) (pre_w NULL: skipped).  gnorm cuts a
+ * row into `groups` equal consecutive pieces and divides each by its own sqrt(mean(piece^2) + eps).  y, weights and act are `dtype`. */
+typedef struct b200_depth_residual_args {
+  const void* y; const void* post_w;
+  const float* x_in; float* x_out;
+  const float* stack; int64_t stack_stride; const void* depth_w; float* avg;
+  const void* pre_w; void* act;
+  int64_t rows; int d, groups, m; float eps; int dtype;
+} b200_depth_residual_args;
+int b200_depth_residual(const b200_depth_residual_args* args, b200_stream_t stream);
+/* One group of heads of b200_head_rope: head h of a row is `dim` numbers at in + row * ld_in + h * in_stride and goes to
+ * out + out_rows[row] * ld_out + h * out_stride (out_rows NULL: the row itself; a row < 0 is skipped; in place allowed).  norm_w
+ * (dim numbers, NULL: no norm) is the weight of an RMS norm over the head; dimensions [rot_off, rot_off + rot_dims) turn by
+ * position * freq[i] (fp32), pair i = (2 i, 2 i + 1) when interleaved, else (i, i + rot_dims / 2), cos and sin times mag. */
+typedef struct b200_head_rope_seg {
+  const void* in; void* out; const void* norm_w; const float* freq; const int64_t* out_rows;
+  int64_t ld_in, ld_out;
+  int heads, dim, in_stride, out_stride, rot_off, rot_dims, interleaved;
+  float mag;
+} b200_head_rope_seg;
+int b200_head_rope(const b200_head_rope_seg* segs, int n_segs, const int32_t* row_pos, int64_t rows, float eps, int dtype, b200_stream_t stream);
+/* Causal attention over cached keys and values in which the heads' scores are mixed before the softmax:
+ *   s_g(i, j) = scale * q_g(i) . k_{g / (n_head / n_kv_head)}(j);  s'_h = sum_g talk[h, g] s_g;  p_h = exp(s'_h) / (exp(sink_h) + sum_j exp(s'_h))
+ * (talk NULL: no mixing; sink NULL: an ordinary softmax).  q (rows, n_head * dk); sequence s = seqs[s] (first row, rows, first position,
+ * cache slot) reads positions 0 .. of its slot: key row p at k_cache + (slot * max_seq + p) * ldk, value row likewise (its own rows
+ * already stored).  n_split CTAs share the keys of one query tile; the workspace holds their partial results. */
+typedef struct b200_talk_attn_args {
+  const void* q; int64_t ldq;
+  const void* k_cache; int64_t ldk; const void* v_cache; int64_t ldv;
+  const void* talk; const void* sink;
+  void* out; int64_t ldo;
+  const int32_t* seqs; int n_seqs, max_q_len;
+  int64_t rows;
+  int n_head, n_kv_head, dk, dv, max_seq, n_split;
+  float scale; int dtype;
+  void* workspace; size_t workspace_bytes;
+} b200_talk_attn_args;
+size_t b200_talk_attn_workspace_bytes(int64_t rows, int n_head, int dv, int n_split);
+int b200_talk_attn(const b200_talk_attn_args* args, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -83,14 +83,35 @@ class LatentPrefillArgs(ctypes.Structure):  # mirrors b200_latent_prefill_args
     _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p),
                 ("ldq", c_int64), ("ldk", c_int64), ("ldv", c_int64), ("ldo", c_int64), ("seqs", c_void_p),
                 ("n_seqs", c_int), ("max_q_len", c_int), ("n_head", c_int), ("dk", c_int), ("dv", c_int),
-                ("scale", c_float), ("dtype", c_int)]
+                ("scale", c_float), ("dtype", c_int),
+                ("k2", c_void_p), ("ldk2", c_int64), ("dk2", c_int), ("sink", c_void_p), ("gate", c_void_p), ("ldg", c_int64), ("gate_mode", c_int)]
 
 
 class LatentDecodeArgs(ctypes.Structure):  # mirrors b200_latent_decode_args
     _fields_ = [("q", c_void_p), ("w_uk", c_void_p), ("w_uv", c_void_p), ("cache", c_void_p), ("out", c_void_p),
                 ("ldq", c_int64), ("ldo", c_int64), ("slot_stride", c_int64), ("row_slot", c_void_p), ("row_pos", c_void_p),
                 ("batch", c_int), ("n_head", c_int), ("dk", c_int), ("dv", c_int), ("r", c_int), ("max_seq", c_int), ("n_split", c_int),
-                ("scale", c_float), ("dtype", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
+                ("scale", c_float), ("dtype", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+                ("dk2", c_int), ("sink", c_void_p), ("gate", c_void_p), ("ldg", c_int64), ("gate_mode", c_int)]
+
+
+class DepthResidualArgs(ctypes.Structure):  # mirrors b200_depth_residual_args
+    _fields_ = [("y", c_void_p), ("post_w", c_void_p), ("x_in", c_void_p), ("x_out", c_void_p), ("stack", c_void_p), ("stack_stride", c_int64),
+                ("depth_w", c_void_p), ("avg", c_void_p), ("pre_w", c_void_p), ("act", c_void_p), ("rows", c_int64), ("d", c_int), ("groups", c_int),
+                ("m", c_int), ("eps", c_float), ("dtype", c_int)]
+
+
+class HeadRopeSeg(ctypes.Structure):  # mirrors b200_head_rope_seg
+    _fields_ = [("inp", c_void_p), ("out", c_void_p), ("norm_w", c_void_p), ("freq", c_void_p), ("out_rows", c_void_p), ("ld_in", c_int64),
+                ("ld_out", c_int64), ("heads", c_int), ("dim", c_int), ("in_stride", c_int), ("out_stride", c_int), ("rot_off", c_int),
+                ("rot_dims", c_int), ("interleaved", c_int), ("mag", c_float)]
+
+
+class TalkAttnArgs(ctypes.Structure):  # mirrors b200_talk_attn_args
+    _fields_ = [("q", c_void_p), ("ldq", c_int64), ("k_cache", c_void_p), ("ldk", c_int64), ("v_cache", c_void_p), ("ldv", c_int64),
+                ("talk", c_void_p), ("sink", c_void_p), ("out", c_void_p), ("ldo", c_int64), ("seqs", c_void_p), ("n_seqs", c_int),
+                ("max_q_len", c_int), ("rows", c_int64), ("n_head", c_int), ("n_kv_head", c_int), ("dk", c_int), ("dv", c_int), ("max_seq", c_int),
+                ("n_split", c_int), ("scale", c_float), ("dtype", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
 
 
 class SandwichArgs(ctypes.Structure):  # mirrors b200_sandwich_args
@@ -124,7 +145,8 @@ ACT_GELU, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = 0, 1, 2, 3
 
 # Entry points of the sources every model needs (library state, norms, sampling) and of the fp32-residual / latent-attention /
 # expert kernels: `load_core()` can serve them from a library built from those sources alone.
-_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu", "attn_prefill.cu", "shortconv.cu", "delta.cu", "window_attn.cu")
+_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu", "attn_prefill.cu", "shortconv.cu", "delta.cu", "window_attn.cu",
+                 "depth.cu", "rope.cu", "talk_attn.cu")
 _CORE_SIGNATURES = {
     "b200_embed_pos": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_rms_rows": (c_int, [ctypes.POINTER(RmsRowsSeg), c_int, c_int64, c_float, c_int, c_int, c_void_p]),
@@ -156,6 +178,10 @@ _CORE_SIGNATURES = {
                                      c_void_p]),
     "b200_window_attn": (c_int, [ctypes.POINTER(WindowAttnArgs), c_void_p]),
     "b200_window_attn_tune": (c_int, [c_int]),
+    "b200_depth_residual": (c_int, [ctypes.POINTER(DepthResidualArgs), c_void_p]),
+    "b200_head_rope": (c_int, [ctypes.POINTER(HeadRopeSeg), c_int, c_void_p, c_int64, c_float, c_int, c_void_p]),
+    "b200_talk_attn_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int]),
+    "b200_talk_attn": (c_int, [ctypes.POINTER(TalkAttnArgs), c_void_p]),
     "b200_attn_prefill_window": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,
                                          c_int, c_float, c_int, c_void_p, c_void_p]),
     "b200_ring_store": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,

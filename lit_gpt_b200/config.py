@@ -277,9 +277,10 @@ class PomipelConfig:
 
 @dataclass
 class RotarySpec:
-    """Rotary positions on the first `dims` dimensions of a head, interleaved pairs (2i, 2i + 1), frequency base^(-2i / dims);
-    with `factor` set the frequencies are blended towards f / factor over a ramp between the dimensions whose wavelength
-    fits `fast` and `slow` times into `original` positions (YaRN), and cos / sin are scaled by 0.1 ln(factor) + 1."""
+    """Rotary positions on the first `dims` dimensions of a head, frequency base^(-2i / dims) for pair i; pairs are (2i, 2i + 1)
+    when `interleaved`, else (i, i + dims / 2).  With `factor` set the frequencies are blended towards f / factor over a ramp
+    between the dimensions whose wavelength fits `fast` and `slow` times into `original` positions (YaRN), and cos / sin are
+    scaled by 0.1 ln(factor) + 1."""
 
     dims: int
     base: float
@@ -287,6 +288,14 @@ class RotarySpec:
     original: float = 0.0
     fast: float = 32.0
     slow: float = 1.0
+    interleaved: bool = True
+
+    @classmethod
+    def from_dict(cls, rot: Dict[str, Any], interleaved: bool = True) -> "RotarySpec":
+        sc = rot.get("scaling") or {}
+        return cls(dims=int(rot["dims"]), base=float(rot["base"]), factor=float(sc["factor"]) if sc else None,
+                   original=float(sc.get("original", 0.0)), fast=float(sc.get("fast", 32.0)), slow=float(sc.get("slow", 1.0)),
+                   interleaved=interleaved)
 
     def frequencies(self) -> List[float]:
         """Angular frequency of every pair, as Python floats (double precision)."""
@@ -475,9 +484,125 @@ class LefalixConfig:
             return cls.from_dict(json.load(fp))
 
 
+@dataclass
+class RotaryLatentSpec:
+    """Latent attention with a rotated key part: queries through a q_rank bottleneck, per head `dim` unrotated and `rot_dim` rotated
+    query / key numbers; the unrotated keys and the values are up-projected from a cached kv_rank latent, the rotated key part is
+    one vector per position shared by all heads and cached beside the latent.  `sink`: a learned logit per head in the softmax
+    denominator; `gate`: sigmoid output gate per output number ("element") or per head ("head") or none."""
+
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    rot: RotarySpec
+    sink: bool = False
+    gate: Optional[str] = None
+    kv_from: Optional[int] = None
+
+
+@dataclass
+class TalkingMixerSpec:
+    """Grouped-head attention with biased projections, a weighted RMS norm on every query and key head before the rotation,
+    scores mixed over the heads by an (heads, heads) matrix before the softmax, and a softmax sink of logit `sink_logit` (0: an
+    extra 1 in the denominator; None: none)."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[RotarySpec] = None
+    sink_logit: Optional[float] = 0.0
+
+
+@dataclass
+class FizadraLayerSpec:
+    type: str                      # "latent_attention" | "latent_attention_2" | "attention"
+    mixer: Any
+    mlp: Optional[DenseMLPSpec] = None
+
+
+@dataclass
+class FizadraConfig:
+    """Fizadra: blocks with grouped RMS norms before and after each sublayer over an fp32 residual stream; what a layer hands on
+    is a learned weighted sum of the embedding and every layer's own result so far.  Mixers: two kinds of latent attention with a
+    rotated key part (interleaved pairs, blended frequencies, sink and per-number gate; or half-split pairs and a per-head gate)
+    and grouped-head attention with mixed scores; feed-forwards dense with squared relu, or none."""
+
+    name: str = "Fizadra"
+    vocab_size: int = 0
+    n_embd: int = 0
+    norm_eps: float = 1e-5
+    norm_groups: int = 1
+    layers: List[FizadraLayerSpec] = field(default_factory=list)
+    block_size: int = 1 << 20      # no position table: the bound of a sequence is what the cache is sized for
+
+    def __post_init__(self) -> None:
+        self.padded_vocab_size = self.vocab_size
+        self.n_layer = len(self.layers)
+        if self.norm_groups < 1 or self.n_embd % self.norm_groups:
+            raise ValueError(f"{self.norm_groups} norm groups do not divide the width {self.n_embd}")
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            if layer.type in ("latent_attention", "latent_attention_2"):
+                if m.rot.dims != m.rot_dim or m.rot_dim % 2:
+                    raise ValueError(f"layer {i}: the rotated part must be rotated whole and have an even size")
+                src = m.kv_from
+                if src is not None:
+                    other = self.layers[src].mixer if 0 <= src < i else None
+                    if not isinstance(other, RotaryLatentSpec) or other.kv_from is not None:
+                        raise ValueError(f"layer {i}: kv_from must name an earlier latent-attention layer that projects its own latents")
+                    if (other.kv_rank, other.rot_dim, other.rot) != (m.kv_rank, m.rot_dim, m.rot):
+                        raise ValueError(f"layer {i}: latent size or rotation differ from those of layer {src}, whose cache it reads")
+            elif layer.type == "attention":
+                if m.heads % m.kv_heads:
+                    raise ValueError(f"layer {i}: {m.kv_heads} key heads do not divide {m.heads} query heads")
+                if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim):
+                    raise ValueError(f"layer {i}: rotary dimensions must be even and at most the head size")
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {layer.type!r}")
+
+    @classmethod
+    def from_dict(cls, js: Dict[str, Any]) -> "FizadraConfig":
+        layers = []
+        for i, entry in enumerate(js["layers"]):
+            mx, kind = entry["mixer"], entry["type"]
+            if kind in ("latent_attention", "latent_attention_2"):
+                second = kind == "latent_attention_2"
+                mixer: Any = RotaryLatentSpec(
+                    heads=int(mx["heads"]), dim=int(mx["dim"]), rot_dim=int(mx["rot_dim"]), vdim=int(mx["vdim"]), kv_rank=int(mx["kv_rank"]),
+                    q_rank=int(mx["q_rank"]), scale=float(mx["scale"]), rot=RotarySpec.from_dict(mx["rot"], interleaved=not second),
+                    sink=not second, gate="head" if second else "element", kv_from=None if mx.get("kv_from") is None else int(mx["kv_from"]))
+            elif kind == "attention":
+                rot = mx.get("rot")
+                mixer = TalkingMixerSpec(heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
+                                         vdim=int(mx.get("vdim", mx["dim"])), scale=float(mx["scale"]),
+                                         rot=RotarySpec.from_dict(rot, interleaved=False) if rot and int(rot["dims"]) > 0 else None)
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            mlp = None
+            if entry.get("mlp") is not None:
+                if entry["mlp"].get("kind", "dense") != "dense":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {entry['mlp'].get('kind')!r}")
+                mlp = DenseMLPSpec(ff=int(entry["mlp"]["ff"]))
+            layers.append(FizadraLayerSpec(type=kind, mixer=mixer, mlp=mlp))
+        return cls(name=js.get("architecture", "Fizadra"), vocab_size=int(js["vocab"]), n_embd=int(js["width"]), norm_eps=float(js["norm"]["eps"]),
+                   norm_groups=int(js["norm"].get("groups", 1)), layers=layers)
+
+    @classmethod
+    def from_json(cls, path: Union[str, Path]) -> "FizadraConfig":
+        with open(path, encoding="utf-8") as fp:
+            return cls.from_dict(json.load(fp))
+
+
 # "architecture" value of config.json -> (configuration class, "module:class" of the model)
 architectures: Dict[str, Any] = {"Pomipel": (PomipelConfig, "lit_gpt_b200.pomipel:Pomipel"),
-                                 "Lefalix": (LefalixConfig, "lit_gpt_b200.lefalix:Lefalix")}
+                                 "Lefalix": (LefalixConfig, "lit_gpt_b200.lefalix:Lefalix"),
+                                 "Fizadra": (FizadraConfig, "lit_gpt_b200.fizadra:Fizadra")}
 
 
 def load_config(checkpoint_dir: Union[str, Path], **kwargs: Any) -> Any:

@@ -1,6 +1,9 @@
 // Latent attention: attention whose keys and values are up-projections of one small cached vector per position
-// (the "latent" c, r numbers), with no rotation.  Per head h: k = W_uk[h] c, v = W_uv[h] c, score = (q_h . k) * scale,
-// causal softmax in fp32.  Only c is cached, so a layer may attend over ANOTHER layer's latents with its own W_uk / W_uv.
+// (the "latent" c, r numbers).  Per head h: k = W_uk[h] c, v = W_uv[h] c, score = (q_h . k) * scale, causal softmax in fp32.
+// Only c is cached, so a layer may attend over ANOTHER layer's latents with its own W_uk / W_uv.
+// Optional parts, each a parameter: a second key part shared by all heads (e.g. rotated dimensions: the query head is then
+// [dk unrotated | dk2 shared-part] numbers and the cache row [c | shared part], rotated before it is stored), a per-head sink
+// logit that joins the softmax denominator only, and a sigmoid output gate per head or per output number.
 //
 // Two kernels families:
 //  * prefill (many query rows per sequence): K and V of the context are expanded by a matrix product outside; the kernel
@@ -39,7 +42,11 @@ template <typename T>
 __global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k,
                                                                      int64_t ldk, const T* __restrict__ v, int64_t ldv,
                                                                      const int4* __restrict__ seqs, T* __restrict__ out, int64_t ldo,
-                                                                     int n_head, int dk, int dv, float scale_log2) {
+                                                                     int n_head, int dk, int dv, float scale_log2,
+                                                                     const T* __restrict__ k2, int64_t ldk2, int dk2,
+                                                                     const T* __restrict__ sink, const T* __restrict__ gate, int64_t ldg,
+                                                                     int gate_mode) {
+  // dk counts the whole query head; its last dk2 numbers meet the shared key part k2 (one per position, the same for every head)
   extern __shared__ __align__(16) float lp_smem[];
   griddep_launch();
   griddep_wait();
@@ -50,7 +57,7 @@ __global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __r
   const int nchunk = (dv + kLpDV - 1) / kLpDV;
   const int h = (int)blockIdx.y / nchunk, c0 = ((int)blockIdx.y % nchunk) * kLpDV;
   const int dvc = min(kLpDV, dv - c0);
-  const int dkp = conflict_free_pitch(dk);
+  const int dkp = conflict_free_pitch(dk), dk1 = dk - dk2;
   constexpr int PP = kLpBN + 4;                       // pitch of the probability tile (68: 17 is odd)
   float* const Qs = lp_smem;                          // [64][dkp]
   float* const Ks = Qs + kLpBM * dkp;                 // [64][dkp]
@@ -83,7 +90,9 @@ __global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __r
     for (int idx = tid; idx < kLpBN * dkp; idx += kLpThreads) {
       const int j = idx / dkp, d = idx - j * dkp;
       float val = 0.f;
-      if (j0 + j < n_keys && d < dk) val = load_as_float(k, (int64_t)(kvstart + j0 + j) * ldk + (int64_t)h * dk + d);
+      if (j0 + j < n_keys && d < dk)
+        val = d < dk1 ? load_as_float(k, (int64_t)(kvstart + j0 + j) * ldk + (int64_t)h * dk1 + d)
+                      : load_as_float(k2, (int64_t)(kvstart + j0 + j) * ldk2 + (d - dk1));
       Ks[idx] = val;
     }
     for (int idx = tid; idx < kLpBN * kLpDV; idx += kLpThreads) {
@@ -170,12 +179,20 @@ __global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __r
   for (int a = 0; a < 4; ++a) {
     const int i = r0 + ty + 16 * a;
     if (i >= qlen) continue;
-    const float inv = 1.0f / l_run[a];
+    float den = l_run[a];
+    if (sink) den += exp2f(load_as_float(sink, h) * 1.4426950408889634f - m_run[a]);   // the sink has no key and no value
+    float inv = 1.0f / den;
+    const T* grow = gate ? gate + (int64_t)(qstart + i) * ldg : nullptr;
+    if (gate_mode == 1) inv *= 1.0f / (1.0f + expf(-load_as_float(grow, h)));
     T* orow = out + (int64_t)(qstart + i) * ldo + (int64_t)h * dv + c0;
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
       const int c = (b < 4 ? 0 : 64) + 4 * tx + (b & 3);
-      if (c < dvc) store_from_float(orow, c, o[a][b] * inv);
+      if (c < dvc) {
+        float val = o[a][b] * inv;
+        if (gate_mode == 2) val *= 1.0f / (1.0f + expf(-load_as_float(grow, (int64_t)h * dv + c0 + c)));
+        store_from_float(orow, c, val);
+      }
     }
   }
 }
@@ -195,7 +212,9 @@ __host__ __device__ inline int absorb_chunks(int r) { return max(1, min(kAbMaxCh
 // grid (n_head, batch, absorb_chunks(r)): every CTA takes a range of column pairs
 template <typename T>
 __global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
-                                                                    float* __restrict__ qlat, int dk, int r, float scale_log2) {
+                                                                    float* __restrict__ qlat, int dk, int r, float scale_log2, int dk2) {
+  // a query head is [dk | dk2]: the first part is absorbed into latent space, the second meets the shared key part stored
+  // behind the latent in every cache row, so q' = [W_uk^T q_a | q_b] has r + dk2 numbers
   extern __shared__ __align__(16) float ab_smem[];   // [dk] query, then [groups][2 * ncol] partial sums
   griddep_launch();
   griddep_wait();
@@ -205,7 +224,11 @@ __global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __re
   const int pair0 = (int)blockIdx.z * ncol;
   const int groups = ncol >= kAbThreads ? 1 : min(kAbThreads / ncol, dk);
   float* const part = ab_smem + dk;
-  for (int d = tid; d < dk; d += kAbThreads) ab_smem[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
+  const T* qh = q + (int64_t)b * ldq + (int64_t)h * (dk + dk2);
+  const int R = r + dk2;
+  for (int d = tid; d < dk; d += kAbThreads) ab_smem[d] = load_as_float(qh, d);
+  if (blockIdx.z == 0)
+    for (int d = tid; d < dk2; d += kAbThreads) qlat[((int64_t)b * n_head + h) * R + r + d] = load_as_float(qh, dk + d) * scale_log2;
   __syncthreads();
   const T* w = w_uk + (int64_t)h * dk * r;
   const int per = (dk + groups - 1) / groups;
@@ -231,7 +254,7 @@ __global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __re
     if (rr >= r) continue;
     float acc = 0.f;
     for (int g = 0; g < groups; ++g) acc += part[g * 2 * ncol + lc];
-    qlat[((int64_t)b * n_head + h) * r + rr] = acc * scale_log2;
+    qlat[((int64_t)b * n_head + h) * R + rr] = acc * scale_log2;
   }
 }
 
@@ -241,14 +264,15 @@ template <typename T>
 __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const float* __restrict__ qlat, const T* __restrict__ cache,
                                                                           int64_t slot_stride, const int* __restrict__ row_slot,
                                                                           const int* __restrict__ row_pos, float* __restrict__ ws, int n_head,
-                                                                          int r, int max_seq) {
+                                                                          int r, int max_seq, int R) {
+  // R >= r: numbers per cache row and per q' (the latent, then a key part that enters the scores only)
   extern __shared__ __align__(16) unsigned char ld_smem_raw[];
   griddep_launch();
   griddep_wait();
-  float* const ql = reinterpret_cast<float*>(ld_smem_raw);    // [r]  q'
-  float* const sc = ql + r;                                    // [32] scores, then probabilities
+  float* const ql = reinterpret_cast<float*>(ld_smem_raw);    // [R]  q'
+  float* const sc = ql + R;                                    // [32] scores, then probabilities
   float* const st = sc + kLdTile;                              // [4]  running max, sum, rescale factor
-  T* const cs = reinterpret_cast<T*>(st + 4);                  // [32][r]
+  T* const cs = reinterpret_cast<T*>(st + 4);                  // [32][R]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, n_split = gridDim.x, h = blockIdx.y, b = blockIdx.z;
   int ctx = row_pos[b] + 1;
@@ -258,7 +282,7 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const f
   const int k0 = split * per, k1 = min(ctx, k0 + per);
   const T* crow = cache + (int64_t)row_slot[b] * slot_stride;
 
-  for (int rr = tid; rr < r; rr += kLdThreads) ql[rr] = qlat[((int64_t)b * n_head + h) * r + rr];
+  for (int rr = tid; rr < R; rr += kLdThreads) ql[rr] = qlat[((int64_t)b * n_head + h) * R + rr];
   if (tid == 0) { st[0] = -INFINITY; st[1] = 0.f; st[2] = 1.f; }
   float o[kLdMaxRPT];
 #pragma unroll
@@ -267,12 +291,12 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const f
   for (int j0 = k0; j0 < k1; j0 += kLdTile) {
     __syncthreads();   // previous tile consumed; ql visible on the first pass
     const int nj = min(kLdTile, k1 - j0);
-    for (int idx = tid; idx < nj * r; idx += kLdThreads) cs[idx] = crow[(int64_t)j0 * r + idx];
+    for (int idx = tid; idx < nj * R; idx += kLdThreads) cs[idx] = crow[(int64_t)j0 * R + idx];
     __syncthreads();
     for (int j = warp; j < kLdTile; j += kLdThreads / 32) {
       float dot = 0.f;
       if (j < nj)
-        for (int rr = lane; rr < r; rr += 32) dot = fmaf(ql[rr], load_as_float(cs, (int64_t)j * r + rr), dot);
+        for (int rr = lane; rr < R; rr += 32) dot = fmaf(ql[rr], load_as_float(cs, (int64_t)j * R + rr), dot);
       dot = warp_sum(dot);
       if (lane == 0) sc[j] = j < nj ? dot : -INFINITY;
     }
@@ -299,7 +323,7 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const f
       const int rr = tid + i * kLdThreads;
       if (rr < r) {
         float acc = o[i] * a;
-        for (int j = 0; j < nj; ++j) acc = fmaf(sc[j], load_as_float(cs, (int64_t)j * r + rr), acc);
+        for (int j = 0; j < nj; ++j) acc = fmaf(sc[j], load_as_float(cs, (int64_t)j * R + rr), acc);
         o[i] = acc;
       }
     }
@@ -314,7 +338,7 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const f
   if (tid == 0) { dst[r] = st[0]; dst[r + 1] = st[1]; }
 }
 
-// The same split on the tensor cores (bf16, r a multiple of 32, r <= 512): one CTA takes 16 heads of one sequence, so the
+// The same split on the tensor cores (bf16, r and R multiples of 32, r <= 512): one CTA takes 16 heads of one sequence, so the
 // scores of a 32-key tile are one (16 x r) . (r x 32) product and the probability-weighted latent sum a (16 x 32) . (32 x r)
 // product, both mma.sync.m16n8k16 with fp32 accumulation; q' and the probabilities are rounded to bf16 as operands.
 // Warp w computes the scores of keys 8 w .. 8 w + 7 and owns columns [w r / 4, (w + 1) r / 4) of the latent sum.
@@ -324,11 +348,11 @@ constexpr int kLmHeads = 16, kLmMaxNT = 16;
 __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const float* __restrict__ qlat, const __nv_bfloat16* __restrict__ cache,
                                                                         int64_t slot_stride, const int* __restrict__ row_slot,
                                                                         const int* __restrict__ row_pos, float* __restrict__ ws, int n_head,
-                                                                        int r, int max_seq) {
+                                                                        int r, int max_seq, int R) {
   extern __shared__ __align__(16) unsigned char lm_smem_raw[];
   griddep_launch();
   griddep_wait();
-  const int pitch = r + 8;                                              // bf16 elements; rows stay 16-byte aligned and spread over the banks
+  const int pitch = R + 8;                                              // bf16 elements; rows stay 16-byte aligned and spread over the banks
   __nv_bfloat16* const Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem_raw);   // [16][pitch]
   __nv_bfloat16* const Cbuf = Qs + kLmHeads * pitch;                          // [2][32][pitch]: the tile in use and the next one
   __nv_bfloat16* const Ps = Cbuf + 2 * kLdTile * pitch;                       // [16][40]
@@ -343,22 +367,22 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const flo
   const int k0 = split * per, k1 = min(ctx, k0 + per);
   const __nv_bfloat16* crow = cache + (int64_t)row_slot[b] * slot_stride;
   const int nt = r / 32;                                                 // 8-column tiles of the latent sum per warp
-  const int chunks = r / 8;                                              // 16-byte chunks per latent
+  const int chunks = R / 8;                                              // 16-byte chunks per cache row
 
   auto load_tile = [&](int j0, int buf) {
     const int nj = min(kLdTile, k1 - j0);
     __nv_bfloat16* dst = Cbuf + buf * kLdTile * pitch;
     for (int idx = tid; idx < kLdTile * chunks; idx += kLdThreads) {
       const int j = idx / chunks, c = idx - j * chunks;
-      pf_cp16(pf_smem(dst + j * pitch + c * 8), crow + (int64_t)(j0 + (j < nj ? j : 0)) * r + c * 8, j < nj);
+      pf_cp16(pf_smem(dst + j * pitch + c * 8), crow + (int64_t)(j0 + (j < nj ? j : 0)) * R + c * 8, j < nj);
     }
     pf_commit();
   };
   if (k0 < k1) load_tile(k0, 0);
-  for (int idx = tid; idx < kLmHeads * (r / 4); idx += kLdThreads) {     // q' of the sixteen heads, four values at a time
-    const int hh = idx / (r / 4), c4 = idx - hh * (r / 4);
+  for (int idx = tid; idx < kLmHeads * (R / 4); idx += kLdThreads) {     // q' of the sixteen heads, four values at a time
+    const int hh = idx / (R / 4), c4 = idx - hh * (R / 4);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (h0 + hh < n_head) v = *reinterpret_cast<const float4*>(qlat + ((int64_t)b * n_head + h0 + hh) * r + 4 * c4);
+    if (h0 + hh < n_head) v = *reinterpret_cast<const float4*>(qlat + ((int64_t)b * n_head + h0 + hh) * R + 4 * c4);
     *reinterpret_cast<uint2*>(Qs + hh * pitch + 4 * c4) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
   }
   float o[kLmMaxNT][4];
@@ -375,7 +399,7 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const flo
     const __nv_bfloat16* Cs = Cbuf + buf * kLdTile * pitch;
     // scores of this warp's eight keys for the sixteen heads
     float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int ks = 0; ks < r / 32; ++ks) {
+    for (int ks = 0; ks < R / 32; ++ks) {
       uint32_t a0[4], a1[4], kb[4];
       ldsm_x4(a0, pf_smem(Qs + (lane & 15) * pitch + ks * 32 + (lane >> 4) * 8));
       ldsm_x4(a1, pf_smem(Qs + (lane & 15) * pitch + ks * 32 + 16 + (lane >> 4) * 8));
@@ -451,7 +475,8 @@ constexpr int kLmThreads = 256;
 template <typename T>
 __global__ void __launch_bounds__(kLmThreads) latent_decode_merge_kernel(const float* __restrict__ ws, const T* __restrict__ w_uv,
                                                                           T* __restrict__ out, int64_t ldo, int n_head, int dv, int r,
-                                                                          int n_split) {
+                                                                          int n_split, const T* __restrict__ sink, const T* __restrict__ gate,
+                                                                          int64_t ldg, int gate_mode) {
   extern __shared__ __align__(16) float lm_smem[];   // [r] averaged latent, [n_split] weights, maxima, sums
   griddep_launch();
   griddep_wait();
@@ -471,9 +496,11 @@ __global__ void __launch_bounds__(kLmThreads) latent_decode_merge_kernel(const f
   for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, smx[s]);
   for (int s = tid; s < n_split; s += kLmThreads) wgt[s] = smx[s] == -INFINITY ? 0.f : exp2f(smx[s] - mx);
   __syncthreads();
-  float tot = 0.f;
+  float tot = sink ? exp2f(load_as_float(sink, h) * 1.4426950408889634f - mx) : 0.f;   // a sink joins the denominator only
   for (int s = 0; s < n_split; ++s) tot = fmaf(wgt[s], ssm[s], tot);
   const float inv = 1.0f / tot;
+  const T* grow = gate_mode ? gate + (int64_t)b * ldg : nullptr;
+  const float head_gate = gate_mode == 1 ? 1.0f / (1.0f + expf(-load_as_float(grow, h))) : 1.0f;
   for (int rr = tid; rr < r; rr += kLmThreads) {
     float acc = 0.f;
 #pragma unroll 8
@@ -486,8 +513,11 @@ __global__ void __launch_bounds__(kLmThreads) latent_decode_merge_kernel(const f
   const int c_lo = (int)blockIdx.z * per, c_hi = min(dv, c_lo + per);
 #pragma unroll 2
   for (int c = c_lo + warp; c < c_hi; c += kLmThreads / 32) {
-    const float dot = warp_dot(w_uv + ((int64_t)h * dv + c) * r, avg, r, lane);
-    if (lane == 0) store_from_float(out, (int64_t)b * ldo + (int64_t)h * dv + c, dot);
+    float dot = warp_dot(w_uv + ((int64_t)h * dv + c) * r, avg, r, lane) * head_gate;
+    if (lane == 0) {
+      if (gate_mode == 2) dot *= 1.0f / (1.0f + expf(-load_as_float(grow, (int64_t)h * dv + c)));
+      store_from_float(out, (int64_t)b * ldo + (int64_t)h * dv + c, dot);
+    }
   }
 }
 
@@ -504,7 +534,8 @@ int prefill_launch(const b200_latent_prefill_args* a, cudaStream_t st) {
   const int nchunk = (a->dv + kLpDV - 1) / kLpDV;
   const dim3 grid((unsigned)((a->max_q_len + kLpBM - 1) / kLpBM), (unsigned)(a->n_head * nchunk), (unsigned)a->n_seqs);
   B200_CUDA(launch(latent_prefill_kernel<T>, grid, dim3(kLpThreads), smem, st, (const T*)a->q, a->ldq, (const T*)a->k, a->ldk, (const T*)a->v,
-                   a->ldv, (const int4*)a->seqs, (T*)a->out, a->ldo, a->n_head, a->dk, a->dv, a->scale * 1.4426950408889634f));
+                   a->ldv, (const int4*)a->seqs, (T*)a->out, a->ldo, a->n_head, a->dk, a->dv, a->scale * 1.4426950408889634f, (const T*)a->k2, a->ldk2,
+                   a->k2 ? a->dk2 : 0, (const T*)a->sink, (const T*)(a->gate_mode ? a->gate : nullptr), a->ldg, a->gate ? a->gate_mode : 0));
   return B200_OK;
 }
 
@@ -515,11 +546,12 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
   const int ab_chunks = absorb_chunks(a->r);
   const int ab_ncol = ((a->r + 1) / 2 + ab_chunks - 1) / ab_chunks;
   const int ab_groups = ab_ncol >= kAbThreads ? 1 : std::min(kAbThreads / ab_ncol, a->dk);
+  const int dk2 = a->dk2 > 0 ? a->dk2 : 0, R = a->r + dk2;   // numbers per cache row and per q'
   const size_t smem0 = ((size_t)a->dk + (size_t)ab_groups * 2 * ab_ncol) * sizeof(float);
-  const size_t smem1 = (size_t)(a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
+  const size_t smem1 = (size_t)(R + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * R * sizeof(T);
   const size_t smem2 = (size_t)(a->r + 4 + 3 * a->n_split) * sizeof(float);
   const int merge_chunks = std::max(1, std::min(4, a->dv / 32));
-  const size_t smem3 = (size_t)((kLmHeads + 2 * kLdTile) * (a->r + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
+  const size_t smem3 = (size_t)((kLmHeads + 2 * kLdTile) * (R + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
   B200_CHECK_ARG(smem0 <= 48 * 1024 && smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "b200_latent_decode: sizes need too much shared memory");
   static PerDeviceOnce once;
   if (once.need()) {
@@ -529,21 +561,23 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
     once.done();
   }
   float* qlat = (float*)a->workspace;
-  float* parts = qlat + (size_t)a->batch * a->n_head * a->r;
+  float* parts = qlat + (size_t)a->batch * a->n_head * R;
   const float scale_log2 = a->scale * 1.4426950408889634f;
   B200_CUDA(launch(latent_absorb_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch, (unsigned)ab_chunks), dim3(kAbThreads), smem0, st, (const T*)a->q, a->ldq,
-                   (const T*)a->w_uk, qlat, a->dk, a->r, scale_log2));
-  const bool tensor = std::is_same<T, __nv_bfloat16>::value && a->r % 32 == 0 && a->r <= 32 * kLmMaxNT && !g_decode_simt.load() &&
+                   (const T*)a->w_uk, qlat, a->dk, a->r, scale_log2, dk2));
+  const bool tensor = std::is_same<T, __nv_bfloat16>::value && a->r % 32 == 0 && R % 32 == 0 && a->r <= 32 * kLmMaxNT && !g_decode_simt.load() &&
+                      smem3 <= 227 * 1024 &&
                       (reinterpret_cast<uintptr_t>(a->cache) & 15) == 0 && (a->slot_stride & 7) == 0;
   if (tensor)
     B200_CUDA(launch(latent_decode_mma_kernel, dim3((unsigned)a->n_split, (unsigned)((a->n_head + kLmHeads - 1) / kLmHeads), (unsigned)a->batch),
                      dim3(kLdThreads), smem3, st, (const float*)qlat, (const __nv_bfloat16*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts,
-                     a->n_head, a->r, a->max_seq));
+                     a->n_head, a->r, a->max_seq, R));
   else
     B200_CUDA(launch(latent_decode_split_kernel<T>, dim3((unsigned)a->n_split, (unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem1, st,
-                     (const float*)qlat, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts, a->n_head, a->r, a->max_seq));
+                     (const float*)qlat, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts, a->n_head, a->r, a->max_seq, R));
   B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch, (unsigned)merge_chunks), dim3(kLmThreads), smem2, st,
-                   (const float*)parts, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split));
+                   (const float*)parts, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split, (const T*)a->sink,
+                   (const T*)(a->gate_mode ? a->gate : nullptr), a->ldg, a->gate ? a->gate_mode : 0));
   return B200_OK;
 }
 
@@ -560,6 +594,9 @@ int b200_latent_prefill(const b200_latent_prefill_args* a, b200_stream_t stream)
   B200_CHECK_ARG(a->n_seqs > 0 && a->n_seqs <= 65535 && a->max_q_len > 0 && a->n_head > 0 && a->dk > 0 && a->dv > 0,
                  "b200_latent_prefill: bad shape");
   B200_CHECK_ARG((int64_t)a->n_head * ((a->dv + kLpDV - 1) / kLpDV) <= 65535, "b200_latent_prefill: too many heads");
+  B200_CHECK_ARG((reinterpret_cast<uintptr_t>(a->seqs) & 15) == 0, "b200_latent_prefill: the sequence table must start on a 16-byte boundary");
+  B200_CHECK_ARG(!a->k2 || (a->dk2 > 0 && a->dk2 < a->dk), "b200_latent_prefill: the shared key part must be shorter than the query head");
+  B200_CHECK_ARG(a->gate_mode >= 0 && a->gate_mode <= 2, "b200_latent_prefill: gate mode 0 (none), 1 (per head) or 2 (per output number)");
   if (a->dtype == B200_BF16) return prefill_launch<__nv_bfloat16>(a, (cudaStream_t)stream);
   if (a->dtype == B200_F32) return prefill_launch<float>(a, (cudaStream_t)stream);
   set_error("b200_latent_prefill: dtype must be bf16 or fp32");
@@ -570,6 +607,7 @@ size_t b200_latent_decode_workspace_bytes(int batch, int n_head, int r, int n_sp
   return ((size_t)batch * n_head * r + (size_t)batch * n_head * n_split * (r + 2)) * sizeof(float);
 }
 
+
 int b200_latent_decode_tune(int force_any_size_kernel) { return b200::g_decode_simt.exchange(force_any_size_kernel ? 1 : 0); }
 
 int b200_latent_decode(const b200_latent_decode_args* a, b200_stream_t stream) {
@@ -578,7 +616,8 @@ int b200_latent_decode(const b200_latent_decode_args* a, b200_stream_t stream) {
   B200_CHECK_ARG(a->batch > 0 && a->batch <= 65535 && a->n_head > 0 && a->n_head <= 65535 && a->dk > 0 && a->dv > 0 && a->r > 0 && a->n_split > 0,
                  "b200_latent_decode: bad shape");
   B200_CHECK_ARG(a->r <= kLdThreads * kLdMaxRPT, "b200_latent_decode: latent size %d above %d", a->r, kLdThreads * kLdMaxRPT);
-  B200_CHECK_ARG(a->workspace_bytes >= b200_latent_decode_workspace_bytes(a->batch, a->n_head, a->r, a->n_split),
+  B200_CHECK_ARG(a->dk2 >= 0 && a->gate_mode >= 0 && a->gate_mode <= 2, "b200_latent_decode: bad shared key part or gate mode");
+  B200_CHECK_ARG(a->workspace_bytes >= b200_latent_decode_workspace_bytes(a->batch, a->n_head, a->r + a->dk2, a->n_split),
                  "b200_latent_decode: workspace too small");
   if (a->dtype == B200_BF16) return decode_launch<__nv_bfloat16>(a, (cudaStream_t)stream);
   if (a->dtype == B200_F32) return decode_launch<float>(a, (cudaStream_t)stream);

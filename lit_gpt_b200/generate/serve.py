@@ -122,6 +122,10 @@ class Replayer:
         from lit_gpt_b200.checkpoint import load_registered
 
         self.model = load_registered(model_dir, dtype=dtype, device=device)
+        bound = self.model.config.block_size
+        if max_tokens and max_tokens < bound:
+            # no request can be longer than what all live requests hold together: caches sized by position need no more than that
+            self.model.max_seq_length = max_tokens
         slots = max(1, min(64, -(-max_tokens // self.model.max_seq_length))) if max_tokens else 2
         self.session = Session(self.model, slots=slots)
 

@@ -587,14 +587,17 @@ def _code(t: torch.Tensor) -> int:
     return C.DTYPE_CODE[t.dtype]
 
 
-def embed_pos(tokens: torch.Tensor, pos: Optional[torch.Tensor], embed: torch.Tensor, pos_table: Optional[torch.Tensor], scale: float):
+def embed_pos(tokens: torch.Tensor, pos: Optional[torch.Tensor], embed: torch.Tensor, pos_table: Optional[torch.Tensor], scale: float,
+              x_out: Optional[torch.Tensor] = None):
     """tokens, pos int32 (n,) -> (x fp32 (n, d), act T (n, d)) with x = embed[tokens] * scale + pos_table[pos]; without a
-    position table (pos None) x = embed[tokens] * scale."""
+    position table (pos None) x = embed[tokens] * scale.  `x_out`: a contiguous fp32 (n, d) tensor to receive x."""
     C.require_cuda(tokens, pos, embed, pos_table)
     if tokens.dtype != torch.int32 or (pos is not None and pos.dtype != torch.int32) or (pos is None and pos_table is not None):
         raise C.B200Error("embed_pos: tokens and pos must be int32")
     n, d = tokens.numel(), embed.shape[1]
-    x = torch.empty((n, d), dtype=torch.float32, device=embed.device)
+    if x_out is not None and (x_out.dtype != torch.float32 or not x_out.is_contiguous() or x_out.numel() != n * d or not x_out.is_cuda):
+        raise C.B200Error("embed_pos: x_out must be a contiguous fp32 (n, d) CUDA tensor")
+    x = x_out if x_out is not None else torch.empty((n, d), dtype=torch.float32, device=embed.device)
     act = torch.empty((n, d), dtype=embed.dtype, device=embed.device)
     C.check(C.load_core().b200_embed_pos(tokens.data_ptr(), C.ptr(pos), embed.data_ptr(), C.ptr(pos_table), float(scale), x.data_ptr(),
                                          act.data_ptr(), n, d, embed.shape[0], 0 if pos_table is None else pos_table.shape[0], _code(embed),
@@ -663,17 +666,35 @@ def scale_f32(t: torch.Tensor, scale: float) -> torch.Tensor:
 LATENT_PREFILL_MMA = True   # tests switch it off to reach the any-size kernel with tensor-core-sized heads
 
 
+def _gate_mode(gate: Optional[torch.Tensor], n_head: int, dv: int) -> int:
+    """0: no gate, 1: one column per head, 2: one column per output number."""
+    if gate is None:
+        return 0
+    if gate.stride(-1) != 1 or gate.shape[-1] not in (n_head, n_head * dv):
+        raise C.B200Error("output gate: rows of one number per head or per output number, unit inner stride")
+    return 2 if gate.shape[-1] == n_head * dv and dv > 1 else 1
+
+
 def latent_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqs: torch.Tensor, max_q_len: int, n_head: int, dk: int, dv: int,
-                   scale: float) -> torch.Tensor:
-    """Ragged causal attention without rotation.  q (n, H * dk); k (m, H * dk) and v (m, H * dv) may be column slices of one
-    buffer; seqs int32 (S, 4) = first query row, query rows, position of the first query row, row of position 0 in k / v."""
-    C.require_cuda(q, k, v, seqs)
+                   scale: float, *, k_shared: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Ragged causal attention over explicit keys and values.  q (n, H * dk); k (m, H * dk) and v (m, H * dv) may be column
+    slices of one buffer; seqs int32 (S, 4) = first query row, query rows, position of the first query row, row of position 0 in
+    k / v.  Optional: `k_shared` (m, dk2), a key part shared by all heads that meets the last dk2 numbers of every query head (k is
+    then (m, H * (dk - dk2))); `sink` (H,), a logit per head in the denominator only; `gate` (n, H) or (n, H * dv), whose sigmoid
+    multiplies the output."""
+    C.require_cuda(q, k, v, seqs, k_shared, sink, gate)
+    if k_shared is not None and (k_shared.dtype != q.dtype or k_shared.stride(-1) != 1):
+        raise C.B200Error("latent_prefill: the shared key part must have the queries' dtype and unit inner stride")
+    if (sink is not None and (sink.dtype != q.dtype or not sink.is_contiguous())) or (gate is not None and gate.dtype != q.dtype):
+        raise C.B200Error("latent_prefill: sink and gate must have the queries' dtype")
+    plain = k_shared is None and sink is None and gate is None
     if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
         raise C.B200Error("latent_prefill: seqs must be contiguous int32 (S, 4)")
     if not (q.dtype == k.dtype == v.dtype) or q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
         raise C.B200Error("latent_prefill: q, k, v of one dtype with unit inner stride")
     out = torch.empty((q.shape[0], n_head * dv), dtype=q.dtype, device=q.device)
-    if (q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and not (q.stride(0) | k.stride(0) | v.stride(0)) & 7
+    if (plain and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and not (q.stride(0) | k.stride(0) | v.stride(0)) & 7
             and not (q.data_ptr() | k.data_ptr() | v.data_ptr() | seqs.data_ptr()) & 15 and LATENT_PREFILL_MMA):
         # tensor-core tiles of the GQA models' prefill kernel, over the packed operands
         C.check(C.load_core().b200_attn_prefill_ragged(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), seqs.data_ptr(),
@@ -682,28 +703,35 @@ def latent_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqs: torc
         return out
     args = C.LatentPrefillArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
                                ldo=out.stride(0), seqs=seqs.data_ptr(), n_seqs=seqs.shape[0], max_q_len=max_q_len, n_head=n_head, dk=dk, dv=dv,
-                               scale=float(scale), dtype=_code(q))
+                               scale=float(scale), dtype=_code(q), k2=C.ptr(k_shared), ldk2=0 if k_shared is None else k_shared.stride(0),
+                               dk2=0 if k_shared is None else k_shared.shape[-1], sink=C.ptr(sink), gate=C.ptr(gate),
+                               ldg=0 if gate is None else gate.stride(0), gate_mode=_gate_mode(gate, n_head, dv))
     C.check(C.load_core().b200_latent_prefill(ctypes.byref(args), C.stream_ptr(q.device)), "latent_prefill")
     return out
 
 
 def latent_decode(q: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, cache: torch.Tensor, row_slot: torch.Tensor, row_pos: torch.Tensor,
-                  n_head: int, dk: int, dv: int, scale: float, n_split: int) -> torch.Tensor:
+                  n_head: int, dk: int, dv: int, scale: float, n_split: int, *, shared_dims: int = 0, sink: Optional[torch.Tensor] = None,
+                  gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One query row per sequence over the cached latents (slots, max_seq, r); row b reads positions 0 .. row_pos[b] of slot
-    row_slot[b].  Returns (B, H * dv)."""
-    C.require_cuda(q, w_uk, w_uv, cache, row_slot, row_pos)
+    row_slot[b].  Returns (B, H * dv).  With `shared_dims` = dk2 > 0 a cache row is [r latent | dk2 shared key part] and a query
+    head [dk | dk2] numbers; `sink` and `gate` as in ``latent_prefill``."""
+    C.require_cuda(q, w_uk, w_uv, cache, row_slot, row_pos, sink, gate)
+    if (sink is not None and (sink.dtype != q.dtype or not sink.is_contiguous())) or (gate is not None and gate.dtype != q.dtype):
+        raise C.B200Error("latent_decode: sink and gate must have the queries' dtype")
     if row_slot.dtype != torch.int32 or row_pos.dtype != torch.int32:
         raise C.B200Error("latent_decode: row_slot and row_pos must be int32")
     if not (q.dtype == w_uk.dtype == w_uv.dtype == cache.dtype) or not (w_uk.is_contiguous() and w_uv.is_contiguous() and cache.is_contiguous()):
         raise C.B200Error("latent_decode: one dtype, contiguous weights and cache")
-    B, r, max_seq = q.shape[0], cache.shape[-1], cache.shape[1]
+    B, r, max_seq = q.shape[0], cache.shape[-1] - shared_dims, cache.shape[1]
     lib = C.load_core()
-    ws = _ws("latent", q.device, lib.b200_latent_decode_workspace_bytes(B, n_head, r, n_split))
+    ws = _ws("latent", q.device, lib.b200_latent_decode_workspace_bytes(B, n_head, r + shared_dims, n_split))
     out = torch.empty((B, n_head * dv), dtype=q.dtype, device=q.device)
     args = C.LatentDecodeArgs(q=q.data_ptr(), w_uk=w_uk.data_ptr(), w_uv=w_uv.data_ptr(), cache=cache.data_ptr(), out=out.data_ptr(), ldq=q.stride(0),
                               ldo=out.stride(0), slot_stride=cache.stride(0), row_slot=row_slot.data_ptr(), row_pos=row_pos.data_ptr(), batch=B,
                               n_head=n_head, dk=dk, dv=dv, r=r, max_seq=max_seq, n_split=n_split, scale=float(scale), dtype=_code(q),
-                              workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+                              workspace=ws.data_ptr(), workspace_bytes=ws.numel(), dk2=shared_dims, sink=C.ptr(sink), gate=C.ptr(gate),
+                              ldg=0 if gate is None else gate.stride(0), gate_mode=_gate_mode(gate, n_head, dv))
     C.check(lib.b200_latent_decode(ctypes.byref(args), C.stream_ptr(q.device)), "latent_decode")
     return out
 
@@ -942,3 +970,81 @@ def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch
 def window_attn_tune(force_tiled_kernel: bool = False) -> bool:
     """Test knob: keep single-row steps on the tiled kernel; returns the previous setting."""
     return bool(C.load_core().b200_window_attn_tune(int(force_tiled_kernel)))
+
+
+# grouped norms with an average over depth, per-head rotation, attention with scores mixed over the heads
+# (csrc/depth.cu, rope.cu, talk_attn.cu)
+# ---------------------------------------------------------------------------------------------------------
+def depth_residual(x_in: torch.Tensor, x_out: torch.Tensor, eps: float, groups: int, *, y: Optional[torch.Tensor] = None,
+                   post_w: Optional[torch.Tensor] = None, stack: Optional[torch.Tensor] = None, m: int = 0, depth_w: Optional[torch.Tensor] = None,
+                   avg: Optional[torch.Tensor] = None, pre_w: Optional[torch.Tensor] = None, act: Optional[torch.Tensor] = None) -> None:
+    """x_out (fp32) = x_in + gnorm(y) * post_w (without y: x_in itself); avg (fp32) = sum_{j < m} depth_w[j] X_j with X_j = stack[j] for
+    j < m - 1 and X_{m-1} = x_out; act = T(gnorm(avg, or x_out) * pre_w).  gnorm divides each of `groups` equal consecutive pieces of
+    a row by its own root mean square.  `stack` (layers, rows, d) fp32; y, the weights and act share the matrix-product dtype."""
+    C.require_cuda(x_in, x_out, y, post_w, stack, depth_w, avg, pre_w, act)
+    for t in (x_in, x_out, stack, avg):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise C.B200Error("depth_residual: the stream, the stack and the average must be contiguous fp32")
+    ref = y if y is not None else (act if act is not None else depth_w)
+    for t in (y, post_w, depth_w, pre_w, act):
+        if t is not None and (t.dtype != ref.dtype or not t.is_contiguous()):
+            raise C.B200Error("depth_residual: branch, weights and act must be contiguous and of one dtype")
+    d = x_in.shape[-1]
+    rows = x_in.numel() // d
+    if avg is not None and (depth_w is None or depth_w.numel() < m or m < 1 or (m > 1 and (stack is None or stack.shape[0] < m - 1))):
+        raise C.B200Error("depth_residual: the average over m results needs m weights and m - 1 earlier results")
+    args = C.DepthResidualArgs(y=C.ptr(y), post_w=C.ptr(post_w), x_in=x_in.data_ptr(), x_out=x_out.data_ptr(), stack=C.ptr(stack),
+                               stack_stride=0 if stack is None else stack.stride(0), depth_w=C.ptr(depth_w), avg=C.ptr(avg), pre_w=C.ptr(pre_w),
+                               act=C.ptr(act), rows=rows, d=d, groups=groups, m=m, eps=float(eps), dtype=C.DTYPE_CODE[ref.dtype])
+    C.check(C.load_core().b200_depth_residual(ctypes.byref(args), C.stream_ptr(x_in.device)), "depth_residual")
+
+
+def rope_seg(inp: torch.Tensor, out: torch.Tensor, heads: int, dim: int, *, norm_w: Optional[torch.Tensor] = None, freq: Optional[torch.Tensor] = None,
+             rot_off: int = 0, rot_dims: int = 0, interleaved: bool = True, mag: float = 1.0, out_rows: Optional[torch.Tensor] = None,
+             in_stride: Optional[int] = None, out_stride: Optional[int] = None) -> "C.HeadRopeSeg":
+    """One group of `heads` heads of `dim` numbers for ``head_rope``: `inp` / `out` are 2-d views (rows, columns) whose first column
+    is the group's first head; heads lie `in_stride` / `out_stride` (default dim) numbers apart.  freq: fp32 (rot_dims / 2,)."""
+    if inp.stride(-1) != 1 or out.stride(-1) != 1 or inp.dtype != out.dtype:
+        raise C.B200Error("head_rope: rows of one dtype with unit inner stride")
+    if freq is not None and (freq.dtype != torch.float32 or not freq.is_contiguous() or freq.numel() < rot_dims // 2):
+        raise C.B200Error("head_rope: frequencies must be contiguous fp32, one per rotated pair")
+    if out_rows is not None and (out_rows.dtype != torch.int64 or not out_rows.is_contiguous()):
+        raise C.B200Error("head_rope: row indices must be contiguous int64")
+    return C.HeadRopeSeg(inp=inp.data_ptr(), out=out.data_ptr(), norm_w=C.ptr(norm_w), freq=C.ptr(freq) if rot_dims else None, out_rows=C.ptr(out_rows),
+                         ld_in=inp.stride(-2), ld_out=out.stride(-2), heads=heads, dim=dim, in_stride=dim if in_stride is None else in_stride,
+                         out_stride=dim if out_stride is None else out_stride, rot_off=rot_off, rot_dims=rot_dims, interleaved=int(interleaved),
+                         mag=float(mag))
+
+
+def head_rope(rows: int, row_pos: torch.Tensor, eps: float, *segs: "C.HeadRopeSeg", dtype: torch.dtype, device: torch.device) -> None:
+    """One launch over `rows` rows for up to three groups of heads built by ``rope_seg``: per head an optional weighted RMS norm, the
+    rotation of a run of its dimensions by the row's position, and the move to its destination (in place, dense, or cache rows)."""
+    if row_pos.dtype != torch.int32 or not row_pos.is_contiguous():
+        raise C.B200Error("head_rope: positions must be contiguous int32")
+    arr = (C.HeadRopeSeg * len(segs))(*segs)
+    C.check(C.load_core().b200_head_rope(arr, len(segs), row_pos.data_ptr(), rows, float(eps), C.DTYPE_CODE[dtype], C.stream_ptr(device)), "head_rope")
+
+
+def talk_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seqs: torch.Tensor, max_q_len: int, n_head: int, n_kv_head: int, dk: int,
+              dv: int, max_seq: int, scale: float, n_split: int = 1, *, talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention over cached keys and values whose scores are mixed over the heads by `talk` (H, H) before the softmax, with an
+    optional sink logit per head.  q (n, H * dk); k_cache / v_cache: 2-d views (slots * max_seq, G * dk | G * dv) of the cache rows;
+    seqs int32 (S, 4) = first row, rows, first position, cache slot.  Returns (n, H * dv)."""
+    C.require_cuda(q, k_cache, v_cache, seqs, talk, sink)
+    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
+        raise C.B200Error("talk_attn: seqs must be contiguous int32 (S, 4)")
+    if not (q.dtype == k_cache.dtype == v_cache.dtype) or q.stride(-1) != 1 or k_cache.stride(-1) != 1 or v_cache.stride(-1) != 1:
+        raise C.B200Error("talk_attn: q and the caches of one dtype with unit inner stride")
+    for t in (talk, sink):
+        if t is not None and (t.dtype != q.dtype or not t.is_contiguous()):
+            raise C.B200Error("talk_attn: talk and sink must be contiguous and of the queries' dtype")
+    n = q.shape[0]
+    lib = C.load_core()
+    ws = _ws("talk", q.device, lib.b200_talk_attn_workspace_bytes(n, n_head, dv, n_split))
+    out = torch.empty((n, n_head * dv), dtype=q.dtype, device=q.device)
+    args = C.TalkAttnArgs(q=q.data_ptr(), ldq=q.stride(0), k_cache=k_cache.data_ptr(), ldk=k_cache.stride(0), v_cache=v_cache.data_ptr(),
+                          ldv=v_cache.stride(0), talk=C.ptr(talk), sink=C.ptr(sink), out=out.data_ptr(), ldo=out.stride(0), seqs=seqs.data_ptr(),
+                          n_seqs=seqs.shape[0], max_q_len=max_q_len, rows=n, n_head=n_head, n_kv_head=n_kv_head, dk=dk, dv=dv, max_seq=max_seq,
+                          n_split=n_split, scale=float(scale), dtype=_code(q), workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    C.check(lib.b200_talk_attn(ctypes.byref(args), C.stream_ptr(q.device)), "talk_attn")
+    return out

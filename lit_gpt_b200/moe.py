@@ -81,12 +81,14 @@ class GatedSparseExperts(nn.Module):
 
 
 class DenseMLP(nn.Module):
-    """W_down act(W_up x) with the exact (erf) gelu; the products are vendor GEMMs, the activation this library's kernel."""
+    """W_down act(W_up x), act = the exact (erf) gelu unless another of ``K.ACT_*`` is named; the products are vendor GEMMs, the
+    activation this library's kernel."""
 
-    def __init__(self, width: int, ff: int) -> None:
+    def __init__(self, width: int, ff: int, activation: int = K.ACT_GELU) -> None:
         super().__init__()
+        self.activation = activation
         self.w_up = nn.Parameter(torch.empty(ff, width), requires_grad=False)
         self.w_down = nn.Parameter(torch.empty(width, ff), requires_grad=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return torch.nn.functional.linear(K.activation_(torch.nn.functional.linear(x, self.w_up), K.ACT_GELU), self.w_down)
+        return torch.nn.functional.linear(K.activation_(torch.nn.functional.linear(x, self.w_up), self.activation), self.w_down)
