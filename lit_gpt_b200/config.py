@@ -556,8 +556,8 @@ class FizadraConfig:
                     other = self.layers[src].mixer if 0 <= src < i else None
                     if not isinstance(other, RotaryLatentSpec) or other.kv_from is not None:
                         raise ValueError(f"layer {i}: kv_from must name an earlier latent-attention layer that projects its own latents")
-                    if (other.kv_rank, other.rot_dim, other.rot) != (m.kv_rank, m.rot_dim, m.rot):
-                        raise ValueError(f"layer {i}: latent size or rotation differ from those of layer {src}, whose cache it reads")
+                    if (other.kv_rank, other.rot_dim) != (m.kv_rank, m.rot_dim):     # the rotated key part is taken as that cache holds it
+                        raise ValueError(f"layer {i}: latent or rotated size differ from those of layer {src}, whose cache it reads")
             elif layer.type == "attention":
                 if m.heads % m.kv_heads:
                     raise ValueError(f"layer {i}: {m.kv_heads} key heads do not divide {m.heads} query heads")
