@@ -780,6 +780,157 @@ def run_lefalix_compare(args) -> None:
                       "gpu_launches": int(K.launch_count() - launches0), "sizes": out}), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --compare fizadra: the Fizadra design beside the closest existing model (Pomipel: the other design with latent attention over an
+# fp32 residual stream) at equal width, heads, head size, latent size and layers; random weights.
+# ---------------------------------------------------------------------------------------------------------
+FIZADRA_SIZES = {
+    # name: width, heads, key-value heads of the mixed-score attention, head size, rotated size, latent size, query latent size, dense ff,
+    #       norm groups; Pomipel's experts, top, expert ff
+    "w1024": (1024, 8, 2, 128, 64, 256, 512, 4096, 4, 16, 4, 512),
+    "w2048": (2048, 16, 4, 128, 64, 512, 1024, 8192, 8, 32, 4, 1024),
+    "w4096": (4096, 32, 8, 128, 64, 512, 1536, 14336, 8, 64, 6, 1024),
+}
+
+
+def run_fizadra_compare(args) -> None:
+    from lit_gpt_b200 import kernels as K
+    from lit_gpt_b200.config import (DenseMLPSpec, FizadraConfig, FizadraLayerSpec, LatentMixerSpec, LayerSpec, MoESpec, PomipelConfig, RotaryLatentSpec,
+                                     RotarySpec, TalkingMixerSpec)
+    from lit_gpt_b200.fizadra import Fizadra
+    from lit_gpt_b200.latent import decode_splits
+    from lit_gpt_b200.pomipel import Pomipel
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_source = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    vocab, T = 32000, args.prompt
+    iters = max(3, min(args.steps, 20))
+    launches0 = K.launch_count()
+    bf = torch.bfloat16
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else FIZADRA_SIZES):
+        d, H, G, hs, dr, r, qr, dff, groups, E, top, ff = FIZADRA_SIZES[name]
+        blended = RotarySpec(dims=dr, base=1e6, factor=4.0, original=4096.0, fast=32.0, slow=1.0)
+        half = RotarySpec(dims=dr, base=1e6, interleaved=False)
+        scale = (hs + dr) ** -0.5
+        layers = [FizadraLayerSpec("latent_attention_2", RotaryLatentSpec(H, hs, dr, hs, r, qr, scale, half, gate="head"), DenseMLPSpec(dff)),
+                  FizadraLayerSpec("latent_attention", RotaryLatentSpec(H, hs, dr, hs, r, qr, scale, blended, sink=True, gate="element"), DenseMLPSpec(dff)),
+                  FizadraLayerSpec("attention", TalkingMixerSpec(H, G, hs, hs, hs ** -0.5, RotarySpec(dims=hs, base=1e6, interleaved=False)), DenseMLPSpec(dff)),
+                  FizadraLayerSpec("latent_attention", RotaryLatentSpec(H, hs, dr, hs, r, qr, scale, blended, sink=True, gate="element", kv_from=1),
+                                   DenseMLPSpec(dff))]
+        fiz = Fizadra(FizadraConfig(vocab_size=vocab, n_embd=d, norm_groups=groups, layers=layers)).to(dev).to(bf).eval()
+        fiz.reset_parameters()
+        fiz.max_seq_length = T + 64
+        players = [LayerSpec("latent_attention", LatentMixerSpec(H, hs, hs, r, qr, hs ** -0.5, None if i % 2 == 0 else i - 1),
+                             MoESpec(E, top, ff, 4, 2)) for i in range(4)]
+        pom = Pomipel(PomipelConfig(vocab_size=vocab, n_embd=d, block_size=T + 64, embedding_scale=d ** 0.5, logit_scale=1.0, layers=players))
+        pom = pom.to(dev).to(bf).eval()
+        pom.reset_parameters()
+        res = {}
+        with torch.inference_mode():
+            for label, model in (("fizadra", fiz), ("pomipel", pom)):
+                for B in (1, 8):
+                    model.set_kv_cache(batch_size=B)
+                    idx = torch.randint(0, vocab, (B, T), device=dev)
+                    pos = torch.arange(T, device=dev)
+                    if B == 1:
+                        ms = _timed(lambda: model(idx, pos), iters, flush)
+                        res[f"{label}_prefill_tok_s"] = round(T / ms * 1e3)
+                    else:
+                        model(idx, pos)
+                    tok, p1 = idx[:, :1].contiguous(), torch.tensor([T], device=dev)
+                    step, graphed = _graphed(lambda: model(tok, p1))
+                    ms = _timed(step, iters, flush)
+                    res[f"{label}_decode_b{B}_tok_s"] = round(B / ms * 1e3)
+                    res[f"{label}_decode_b{B}_graphed"] = graphed
+                    del step
+                model.clear_kv_cache()
+            kern = {}
+            seqs = torch.tensor([[0, T, 0, 0]], dtype=torch.int32, device=dev)
+            pairs = T * (T + 1) / 2
+            # prompt attention over expanded keys and values: the rotated shared key part makes the query head hs + dr wide
+            mx = fiz.blocks[1].mixer
+            q = torch.randn(T, H * (hs + dr), device=dev, dtype=bf)
+            kvp = torch.randn(T, 2 * H * hs, device=dev, dtype=bf)
+            kr = torch.randn(T, dr, device=dev, dtype=bf)
+            gate = torch.randn(T, H * hs, device=dev, dtype=bf)
+            ms = _timed(lambda: K.latent_prefill(q, kvp[:, : H * hs], kvp[:, H * hs :], seqs, T, H, hs + dr, hs, scale, k_shared=kr, sink=mx.sink, gate=gate),
+                        iters, flush)
+            kern["prefill_latent_attention_fizadra"] = {"ms": ms, "frac_of_measured_bf16": 2.0 * H * (2 * hs + dr) * pairs / (ms * 1e-3) / tf}
+            qp = torch.randn(T, H * hs, device=dev, dtype=bf)
+            ms = _timed(lambda: K.latent_prefill(qp, kvp[:, : H * hs], kvp[:, H * hs :], seqs, T, H, hs, hs, hs ** -0.5), iters, flush)
+            kern["prefill_attention_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * H * hs * pairs / (ms * 1e-3) / tf}
+            # prompt attention with mixed scores, over the cache rows
+            ta = fiz.blocks[2].mixer
+            kc, vc = torch.randn(T, G * hs, device=dev, dtype=bf), torch.randn(T, G * hs, device=dev, dtype=bf)
+            ms = _timed(lambda: K.talk_attn(qp, kc, vc, seqs, T, H, G, hs, hs, T, hs ** -0.5, 1, talk=ta.talk, sink=ta.sink), iters, flush)
+            kern["prefill_mixed_score_attention_fizadra"] = {"ms": ms, "frac_of_measured_bf16": (4.0 * H * hs + 2.0 * H * H) * pairs / (ms * 1e-3) / tf}
+            # single rows
+            B = 8
+            slot = torch.arange(B, dtype=torch.int32, device=dev)
+            rp = torch.full((B,), T - 1, dtype=torch.int32, device=dev)
+            qd = torch.randn(B, H * (hs + dr), device=dev, dtype=bf)
+            cache = torch.randn(B, T, r + dr, device=dev, dtype=bf)
+            gd = torch.randn(B, H * hs, device=dev, dtype=bf)
+            tiles = -(-H // 16)
+            ms = _timed(lambda: K.latent_decode(qd, mx.w_uk, mx.w_uv, cache, slot, rp, H, hs, hs, scale, decode_splits(T, B * tiles), shared_dims=dr,
+                                                sink=mx.sink, gate=gd), iters, flush)
+            roof = max(B * T * (r + dr) * 2 / hbm, 2.0 * B * H * T * (2 * r + dr) / tf)
+            kern["decode_latent_attention_fizadra"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": B * T * (r + dr) * 2}
+            pm = pom.blocks[0].mixer
+            qdp, cp = torch.randn(B, H * hs, device=dev, dtype=bf), torch.randn(B, T, r, device=dev, dtype=bf)
+            ms = _timed(lambda: K.latent_decode(qdp, pm.w_uk, pm.w_uv, cp, slot, rp, H, hs, hs, hs ** -0.5, decode_splits(T, B * tiles)), iters, flush)
+            roof = max(B * T * r * 2 / hbm, 4.0 * B * H * T * r / tf)
+            kern["decode_attention_pomipel"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": B * T * r * 2}
+            kcb, vcb = torch.randn(B * T, G * hs, device=dev, dtype=bf), torch.randn(B * T, G * hs, device=dev, dtype=bf)
+            sq1 = torch.tensor([(b, 1, T - 1, b) for b in range(B)], dtype=torch.int32, device=dev)
+            ms = _timed(lambda: K.talk_attn(qdp, kcb, vcb, sq1, 1, H, G, hs, hs, T, hs ** -0.5, decode_splits(T, B), talk=ta.talk, sink=ta.sink), iters, flush)
+            roof = 2.0 * B * T * G * hs * 2 / hbm
+            kern["decode_mixed_score_attention_fizadra"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": 2.0 * B * T * G * hs * 2}
+            # residual kernels: post-norm in groups + sum + sum over five results + next pre-norm, against Pomipel's norm + sum
+            x = torch.randn(T, d, device=dev, dtype=bf)
+            stack = torch.randn(5, T, d, device=dev)
+            xs, avg, act = torch.randn(T, d, device=dev), torch.empty(T, d, device=dev), torch.empty(T, d, device=dev, dtype=bf)
+            blk = fiz.blocks[3]
+            ms = _timed(lambda: K.depth_residual(xs, stack[4], 1e-5, groups, y=x, post_w=blk.norm_2b, stack=stack, m=5, depth_w=blk.dwa, avg=avg,
+                                                 pre_w=blk.norm_1, act=act), iters, flush)
+            kern["residual_with_depth_sum_fizadra"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 4 * 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.depth_residual(xs, xs, 1e-5, groups, y=x, post_w=blk.norm_1b, pre_w=blk.norm_2, act=act), iters, flush)
+            kern["residual_fizadra"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.residual_norm_add(x, pom.blocks[0].norm_1, 1e-5, xs, act), iters, flush)
+            kern["residual_norm_pomipel"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            # per-head norm + rotation + cache store of a fused q | k | v projection, beside Pomipel's norm of projected rows
+            cols = (H + 2 * G) * hs
+            qkv = torch.randn(T, cols, device=dev, dtype=bf)
+            kcache, vcache = torch.empty(T, G * hs, device=dev, dtype=bf), torch.empty(T, G * hs, device=dev, dtype=bf)
+            rows64, pos32 = torch.arange(T, device=dev), torch.arange(T, device=dev, dtype=torch.int32)
+            fr = ta.freq(dev)
+            segs = [K.rope_seg(qkv[:, : H * hs], qkv[:, : H * hs], H, hs, norm_w=ta.q_norm, freq=fr, rot_dims=hs, interleaved=False),
+                    K.rope_seg(qkv[:, H * hs : (H + G) * hs], kcache, G, hs, norm_w=ta.k_norm, freq=fr, rot_dims=hs, interleaved=False, out_rows=rows64),
+                    K.rope_seg(qkv[:, (H + G) * hs :], vcache, G, hs, out_rows=rows64)]
+            ms = _timed(lambda: K.head_rope(T, pos32, 1e-5, *segs, dtype=bf, device=dev), iters, flush)
+            kern["head_norm_rotation_store_fizadra"] = {"ms": ms, "frac_of_measured_hbm": T * cols * 4.0 / (ms * 1e-3) / hbm}
+            down, cq = torch.randn(T, cols, device=dev, dtype=bf), torch.empty(T, cols, device=dev, dtype=bf)
+            wn = torch.ones(cols, device=dev, dtype=bf)
+            ms = _timed(lambda: K.rms_rows(T, 1e-5, K.rms_seg(down, wn, cq, cols, False), in_dtype=bf, out_dtype=bf, device=dev), iters, flush)
+            kern["norm_of_projected_rows_pomipel"] = {"ms": ms, "frac_of_measured_hbm": T * cols * 4.0 / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: fiz.blocks[0].mlp(x), iters, flush)
+            kern["dense_mlp_fizadra"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * dff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: pom.blocks[0].mlp(x), iters, flush)
+            kern["experts_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            res["kernels"] = {k: {a: (round(b, 4) if isinstance(b, float) else b) for a, b in v.items()} for k, v in kern.items()}
+        out[name] = res
+        del fiz, pom
+        torch.cuda.empty_cache()
+    print(json.dumps({"compare": "fizadra", "layers": 4, "prompt": T, "context": T, "dtype": "bf16", "data": "synthetic, random weights",
+                      "l2": "flushed between timed calls", "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                                                                       "source": peak_source},
+                      "gpu_launches": int(K.launch_count() - launches0), "sizes": out}), flush=True)
+
+
 def main() -> None:
     # stdout carries exactly one JSON line: NCCL's own banner / debug lines (when the box sets NCCL_DEBUG) go to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
@@ -793,11 +944,14 @@ def main() -> None:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama2-7b-nf4-bs1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: build fewer blocks (invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--compare", choices=["pomipel", "lefalix"], default=None,
+    ap.add_argument("--compare", choices=["pomipel", "lefalix", "fizadra"], default=None,
                     help="instead of the default workload: prefill / decode throughput of that design beside the closest existing model")
     ap.add_argument("--sizes", default=None, help=f"--compare: comma-separated subset of {sorted(ARCH_SIZES)} (the same names for both designs)")
     ap.add_argument("--prompt", type=int, default=2048, help="--compare: prompt and context length")
     args = ap.parse_args()
+    if args.compare == "fizadra":
+        run_fizadra_compare(args)
+        return
     if args.compare == "lefalix":
         run_lefalix_compare(args)
         return

@@ -115,8 +115,8 @@ class Fizadra(SlotServed, nn.Module):
             elif leaf == "dwa":
                 p.data.zero_()
                 p.data[-1] = 1.0
-            elif leaf == "sink" and "mixer" in name and isinstance(self.get_submodule(name.rsplit(".", 1)[0]), TalkingHeadsAttention):
-                p.data.fill_(float(self.get_submodule(name.rsplit(".", 1)[0]).spec.sink_logit))
+            elif leaf == "sink" and isinstance(self.get_submodule(name.rsplit(".", 1)[0]), TalkingHeadsAttention):
+                p.data.fill_(float(self.get_submodule(name.rsplit(".", 1)[0]).spec.sink_logit))     # a constant of the design
             elif "norm" in leaf:
                 p.data.fill_(1.0)
             elif p.dim() == 1:
