@@ -412,6 +412,12 @@ int b200_latent_prefill(const b200_latent_prefill_args* args, b200_stream_t stre
  * over packed operands): leading dimensions multiples of 8 elements, q / k / v / seqs 16-byte aligned. */
 int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
                              int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int head_size, float scale, b200_stream_t stream);
+/* The same tiles for latent attention with a key part shared by the heads (bf16): q (rows, n_head * (head_size + dk2)), each head laid
+ * out [head_size | dk2]; k, v (context rows, n_head * head_size); k2 (context rows, dk2); head_size and dk2 in {64, 128}; sink, gate and
+ * gate_mode as in b200_latent_prefill_args (NULL / 0: absent). */
+int b200_attn_prefill_shared(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const void* k2, int64_t ldk2,
+                             int dk2, const int32_t* seqs, int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int head_size, float scale,
+                             const void* sink, const void* gate, int64_t ldg, int gate_mode, b200_stream_t stream);
 /* One query row per sequence over cached latents (slots, max_seq, r): sequence b reads positions 0 .. row_pos[b] of slot
  * row_slot[b] (its own latent already stored).  w_uk (n_head * dk, r) and w_uv (n_head * dv, r) are absorbed: no keys or
  * values are materialised.  n_split CTAs share each (sequence, head); the workspace holds their partial results. */

@@ -157,6 +157,8 @@ _CORE_SIGNATURES = {
     "b200_latent_prefill": (c_int, [ctypes.POINTER(LatentPrefillArgs), c_void_p]),
     "b200_attn_prefill_ragged": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,
                                          c_float, c_void_p]),
+    "b200_attn_prefill_shared": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_int,
+                                         c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200_latent_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200_latent_decode": (c_int, [ctypes.POINTER(LatentDecodeArgs), c_void_p]),
     "b200_latent_decode_tune": (c_int, [c_int]),

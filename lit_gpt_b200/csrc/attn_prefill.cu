@@ -36,9 +36,17 @@ struct PfView {
   int window;
   const __nv_bfloat16* sink;
   int kv_first_row;
+  // ragged only, kernels instantiated with HK2 > 0: a second key part of HK2 numbers per position shared by all heads (k2, rows k2_r
+  // apart, the same rows as k), met by columns [HS, HS + HK2) of each query head.  gate: rows gate_r apart; the output is multiplied
+  // by sigmoid(gate[row, h]) (gate_mode 1) or sigmoid(gate[row, h * HS + c]) (gate_mode 2).
+  const __nv_bfloat16* k2;
+  int64_t k2_r;
+  const __nv_bfloat16* gate;
+  int64_t gate_r;
+  int gate_mode;
 };
 
-template <int HS, typename PosT>
+template <int HS, typename PosT, int HK2 = 0>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                     const PosT* __restrict__ pos, __nv_bfloat16* __restrict__ y, int T, int n_head, int n_groups, int max_seq,
@@ -49,6 +57,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   uint8_t* const sQ = pf_smem_raw;                   // [128][HS]
   uint8_t* const sK = sQ + QB;                       // [2][64][HS]
   uint8_t* const sV = sK + 2 * KB;                   // [2][64][HS]
+  constexpr int CH2 = HK2 / 8, KB2 = kPfBN * HK2 * 2;
+  uint8_t* const sQ2 = sV + 2 * KB;                  // [128][HK2]  the query columns that meet the shared key part
+  uint8_t* const sK2 = sQ2 + kPfBM * HK2 * 2;        // [2][64][HK2]
   __shared__ int s_maxpos[kPfThreads / 32];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
@@ -73,6 +84,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const __nv_bfloat16* qh = q + (int64_t)b * vw.q_b + (int64_t)h * vw.q_h + qrow0 * vw.q_r;
   const __nv_bfloat16* kg = kc + (int64_t)b * vw.k_b + (int64_t)grp * vw.k_h + kvrow0 * vw.k_r;
   const __nv_bfloat16* vg = vc + (int64_t)b * vw.v_b + (int64_t)grp * vw.v_h + kvrow0 * vw.v_r;
+  const __nv_bfloat16* k2g = HK2 > 0 ? vw.k2 + kvrow0 * vw.k2_r : nullptr;
 
   // this thread's two query rows and their causal limits; the CTA's key range is [0, max limit]
   const int rowA = r0 + warp * 16 + g, rowB = rowA + 8;
@@ -92,6 +104,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int r = i / CH, c = i % CH;
     const bool ok = r0 + r < T;
     pf_cp16(pf_smem(sQ) + sw<HS>(r, c), qh + (int64_t)(ok ? r0 + r : 0) * vw.q_r + c * 8, ok);
+  }
+  if constexpr (HK2 > 0) {
+    for (int i = tid; i < kPfBM * CH2; i += kPfThreads) {
+      const int r = i / CH2, c = i % CH2;
+      const bool ok = r0 + r < T;
+      pf_cp16(pf_smem(sQ2) + sw<HK2>(r, c), qh + (int64_t)(ok ? r0 + r : 0) * vw.q_r + HS + c * 8, ok);
+    }
   }
   pf_commit();
   __syncthreads();
@@ -114,6 +133,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       pf_cp16(pf_smem(sK) + buf * KB + sw<HS>(r, c), kg + row * vw.k_r + c * 8, ok);
       pf_cp16(pf_smem(sV) + buf * KB + sw<HS>(r, c), vg + row * vw.v_r + c * 8, ok);
     }
+    if constexpr (HK2 > 0) {
+      for (int i = tid; i < kPfBN * CH2; i += kPfThreads) {
+        const int r = i / CH2, c = i % CH2;
+        const bool ok = j0 + r <= cta_lim;
+        pf_cp16(pf_smem(sK2) + buf * KB2 + sw<HK2>(r, c), k2g + (ok ? j0 + r : 0) * vw.k2_r + c * 8, ok);
+      }
+    }
     pf_commit();
   };
   load_kv(tile_lo, tile_lo & 1);
@@ -130,6 +156,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
   for (int ks = 0; ks < HS / 16; ++ks)
     ldsm_x4(qf[ks], pf_smem(sQ) + sw<HS>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+  uint32_t qf2[HK2 > 0 ? HK2 / 16 : 1][4];
+  if constexpr (HK2 > 0) {
+#pragma unroll
+    for (int ks = 0; ks < HK2 / 16; ++ks)
+      ldsm_x4(qf2[ks], pf_smem(sQ2) + sw<HK2>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+  }
 
   const int warp_lim = wl;
   for (int tile = tile_lo; tile < ntiles; ++tile) {
@@ -150,6 +182,19 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           ldsm_x4(kf, kb + sw<HS>(np * 16 + ((lane >> 4) << 3) + (lane & 7), ks * 2 + ((lane >> 3) & 1)));
           pf_mma(s[2 * np], qf[ks], kf[0], kf[1]);
           pf_mma(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+        }
+      }
+      if constexpr (HK2 > 0) {   // the shared key part's share of the scores
+        const uint32_t kb2 = pf_smem(sK2) + buf * KB2;
+#pragma unroll
+        for (int ks = 0; ks < HK2 / 16; ++ks) {
+#pragma unroll
+          for (int np = 0; np < kPfBN / 16; ++np) {
+            uint32_t kf[4];
+            ldsm_x4(kf, kb2 + sw<HK2>(np * 16 + ((lane >> 4) << 3) + (lane & 7), ks * 2 + ((lane >> 3) & 1)));
+            pf_mma(s[2 * np], qf2[ks], kf[0], kf[1]);
+            pf_mma(s[2 * np + 1], qf2[ks], kf[2], kf[3]);
+          }
         }
       }
       // causal limit + running maximum
@@ -212,34 +257,49 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     iA = cA / (lA * cA + exp2f(sk - eA));
     iB = cB / (lB * cB + exp2f(sk - eB));
   }
+  const int gmode = vw.seqs && vw.gate ? vw.gate_mode : 0;
+  auto sigm = [](const __nv_bfloat16* p) -> float { return 1.0f / (1.0f + expf(-__bfloat162float(*p))); };
   if (rowA < T) {
     __nv_bfloat16* yr = y + (int64_t)b * vw.y_b + (qrow0 + rowA) * vw.y_r + (int64_t)h * HS;
+    const __nv_bfloat16* gr = gmode ? vw.gate + (qrow0 + rowA) * vw.gate_r : nullptr;
+    if (gmode == 1) iA *= sigm(gr + h);
 #pragma unroll
-    for (int i = 0; i < HS / 8; ++i) *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(o_acc[i][0] * iA, o_acc[i][1] * iA);
+    for (int i = 0; i < HS / 8; ++i) {
+      float a0 = o_acc[i][0] * iA, a1 = o_acc[i][1] * iA;
+      if (gmode == 2) { a0 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq); a1 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq + 1); }
+      *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(a0, a1);
+    }
   }
   if (rowB < T) {
     __nv_bfloat16* yr = y + (int64_t)b * vw.y_b + (qrow0 + rowB) * vw.y_r + (int64_t)h * HS;
+    const __nv_bfloat16* gr = gmode ? vw.gate + (qrow0 + rowB) * vw.gate_r : nullptr;
+    if (gmode == 1) iB *= sigm(gr + h);
 #pragma unroll
-    for (int i = 0; i < HS / 8; ++i) *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(o_acc[i][2] * iB, o_acc[i][3] * iB);
+    for (int i = 0; i < HS / 8; ++i) {
+      float a0 = o_acc[i][2] * iB, a1 = o_acc[i][3] * iB;
+      if (gmode == 2) { a0 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq); a1 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq + 1); }
+      *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(a0, a1);
+    }
   }
 }
 
-template <int HS, typename PosT>
+template <int HS, typename PosT, int HK2 = 0>
 cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const void* pos, void* y, int B, int T, int H, int G, int max_seq,
                            float scale, cudaStream_t st, const PfView* view = nullptr) {
   // default: q (B, H, T, HS), caches (B, G, max_seq, HS), y (B, T, H * HS)
   const PfView vw = view ? *view
                          : PfView{(int64_t)H * T * HS, (int64_t)T * HS, HS, (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS,
-                                  (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr, 0, nullptr, 0};
-  const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2;
+                                  (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr, 0, nullptr, 0,
+                                  nullptr, 0, nullptr, 0, 0};
+  const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2 + (size_t)(kPfBM + 2 * kPfBN) * HK2 * 2;
   static PerDeviceOnce once;
   if (once.need()) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HS, PosT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HS, PosT, HK2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     once.done();
   }
   dim3 grid((T + kPfBM - 1) / kPfBM, H, B);
-  return launch(attn_prefill_kernel<HS, PosT>, grid, dim3(kPfThreads), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
+  return launch(attn_prefill_kernel<HS, PosT, HK2>, grid, dim3(kPfThreads), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
                 (const __nv_bfloat16*)vc, (const PosT*)pos, (__nv_bfloat16*)y, T, H, G, max_seq, scale * 1.4426950408889634f, vw);
 }
 
@@ -278,7 +338,8 @@ extern "C" int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0, "b200_attn_prefill_ragged: leading dimensions must be multiples of 8 elements");
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_ragged: operands must be 16-byte aligned");
-  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0, nullptr, 0};
+  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0, nullptr, 0,
+                  nullptr, 0, nullptr, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
@@ -298,9 +359,36 @@ extern "C" int b200_attn_prefill_window(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_window: operands must be 16-byte aligned");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), window,
-                  reinterpret_cast<const __nv_bfloat16*>(sink), 1};
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, nullptr, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
+  return B200_OK;
+}
+
+// The ragged tiles for latent attention with a key part shared by the heads: q (rows, H * (hs + dk2)) with each head laid out as
+// [hs | dk2]; k, v (context rows, H * hs) expanded per head; k2 (context rows, dk2) the shared part; optional sink logits and a
+// sigmoid output gate (gate_mode 1: one column per head, 2: one per output number).  hs in {64, 128}, dk2 in {64, 128}.
+extern "C" int b200_attn_prefill_shared(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const void* k2,
+                                        int64_t ldk2, int dk2, const int32_t* seqs, int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head,
+                                        int head_size, float scale, const void* sink, const void* gate, int64_t ldg, int gate_mode,
+                                        b200_stream_t stream) {
+  B200_CHECK_ARG(q && k && v && k2 && seqs && y, "b200_attn_prefill_shared: null pointer");
+  B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && n_head > 0 && n_head <= 65535, "b200_attn_prefill_shared: bad shape");
+  B200_CHECK_ARG((head_size == 64 || head_size == 128) && (dk2 == 64 || dk2 == 128), "b200_attn_prefill_shared: sizes must be 64 or 128 (got %d, %d)",
+                 head_size, dk2);
+  B200_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0 || gate), "b200_attn_prefill_shared: bad gate");
+  B200_CHECK_ARG(((ldq | ldk | ldv | ldk2) & 7) == 0 && (ldy & 1) == 0, "b200_attn_prefill_shared: leading dimensions must be multiples of 8 elements");
+  B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(k2) |
+                   reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 3) == 0,
+                 "b200_attn_prefill_shared: operands must be 16-byte aligned");
+  const PfView vw{0, head_size + dk2, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0,
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 0, reinterpret_cast<const __nv_bfloat16*>(k2), ldk2,
+                  reinterpret_cast<const __nv_bfloat16*>(gate), ldg, gate_mode};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (head_size == 128 && dk2 == 64) B200_CUDA((launch_prefill<128, int32_t, 64>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
+  else if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 128>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
+  else if (dk2 == 64) B200_CUDA((launch_prefill<64, int32_t, 64>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
+  else B200_CUDA((launch_prefill<64, int32_t, 128>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   return B200_OK;
 }

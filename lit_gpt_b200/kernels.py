@@ -701,6 +701,16 @@ def latent_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqs: torc
                                                        seqs.shape[0], max_q_len, out.data_ptr(), out.stride(0), n_head, dk, float(scale),
                                                        C.stream_ptr(q.device)), "attn_prefill_ragged")
         return out
+    gm = _gate_mode(gate, n_head, dv)
+    if (k_shared is not None and q.dtype == torch.bfloat16 and LATENT_PREFILL_MMA and dv in (64, 128) and dk - k_shared.shape[-1] == dv
+            and k_shared.shape[-1] in (64, 128) and not (q.stride(0) | k.stride(0) | v.stride(0) | k_shared.stride(0)) & 7
+            and not (q.data_ptr() | k.data_ptr() | v.data_ptr() | k_shared.data_ptr() | seqs.data_ptr()) & 15):
+        # tensor-core tiles with the shared key part as extra columns of the score product
+        C.check(C.load_core().b200_attn_prefill_shared(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_shared.data_ptr(),
+                                                       k_shared.stride(0), k_shared.shape[-1], seqs.data_ptr(), seqs.shape[0], max_q_len, out.data_ptr(),
+                                                       out.stride(0), n_head, dv, float(scale), C.ptr(sink), C.ptr(gate),
+                                                       0 if gate is None else gate.stride(0), gm, C.stream_ptr(q.device)), "attn_prefill_shared")
+        return out
     args = C.LatentPrefillArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
                                ldo=out.stride(0), seqs=seqs.data_ptr(), n_seqs=seqs.shape[0], max_q_len=max_q_len, n_head=n_head, dk=dk, dv=dv,
                                scale=float(scale), dtype=_code(q), k2=C.ptr(k_shared), ldk2=0 if k_shared is None else k_shared.stride(0),

@@ -73,6 +73,17 @@ CFG_WIDE = config(width=64, vocab=120, groups=1, eps=1e-3, layers=[
 ])
 
 
+# head sizes the tensor-core prompt tiles take in bf16: unrotated = value size 64 and 128, rotated part 64 (and 128), a borrowed cache,
+# and an attention layer between them
+CFG_TILES = config(width=96, vocab=140, groups=2, layers=[
+    layer(latent(FIRST, 2, 64, 64, 64, kv_rank=32, q_rank=24, base=1e4, scaling=(4.0, 64, 8.0, 1.0)), 100),
+    layer(latent(SECOND, 3, 128, 64, 128, kv_rank=64, q_rank=48, base=1e5), 120),
+    layer(talking(4, 2, 64, 64, rot_dims=32, base=1e4), None),
+    layer(latent(SECOND, 2, 64, 128, 64, kv_rank=32, q_rank=40, base=1e3), 80),
+    layer(latent(FIRST, 2, 128, 64, 128, kv_rank=64, q_rank=16, base=1e5, scaling=(2.0, 32, 4.0, 1.0), kv_from=1), 64),
+])
+
+
 def checkpoint(cfg, seed, sink_mean=0.5):
     """Random bf16 weights of a size that keeps every mechanism alive."""
     g = torch.Generator().manual_seed(seed)
@@ -258,7 +269,8 @@ def _latent_reference(q, c, kr, w_uk, w_uv, sink, gate, H, dn, dr, dv, scale, st
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(3, 10, 6, 7, 12), (4, 24, 32, 136, 64), (16, 16, 32, 8, 64), (2, 64, 64, 128, 96)])
+@pytest.mark.parametrize("sizes", [(3, 10, 6, 7, 12), (4, 24, 32, 136, 64), (16, 16, 32, 8, 64), (2, 64, 64, 128, 96), (2, 64, 64, 64, 96),
+                                   (3, 128, 64, 128, 64), (2, 64, 128, 64, 32)])
 @pytest.mark.parametrize("options", ["sink+element", "head", "none"])
 def test_latent_attention_kernels_with_a_shared_key_part(dtype, sizes, options):
     """Prompt tiles (a sequence from position 0 and one continuing at position 70, together) and single rows (any-size and, for
@@ -297,9 +309,18 @@ def test_latent_attention_kernels_with_a_shared_key_part(dtype, sizes, options):
     cg = cache.cuda()
     ctx = k.gather_rows(cg.view(-1, r + dr), torch.tensor(ctx_rows, dtype=torch.int64, device="cuda"))
     kv = torch.nn.functional.linear(ctx[:, :r].float(), torch.cat([w_uk, w_uv]).cuda().float()).to(dtype)
-    got = k.latent_prefill(q.cuda(), kv[:, : H * dn], kv[:, H * dn :], torch.tensor(seqs, dtype=torch.int32, device="cuda"), 150, H, dn + dr, dv, scale,
-                           k_shared=ctx[:, r:], sink=None if sink is None else sink.cuda(), gate=None if gate is None else gate_all.cuda()[:, 5:])
-    assert rel_err(got, want) < (tol if dtype == torch.float32 else 4e-2), rel_err(got, want)   # bf16: K and V rounded after the expansion
+    tiles = dtype == torch.bfloat16 and dn == dv and dv in (64, 128) and dr in (64, 128)     # sizes the tensor-core tiles take
+    for mma in ((True, False) if tiles else (True,)):
+        k.LATENT_PREFILL_MMA = mma
+        try:
+            launches = k.launch_count()
+            got = k.latent_prefill(q.cuda(), kv[:, : H * dn], kv[:, H * dn :], torch.tensor(seqs, dtype=torch.int32, device="cuda"), 150, H, dn + dr, dv,
+                                   scale, k_shared=ctx[:, r:], sink=None if sink is None else sink.cuda(),
+                                   gate=None if gate is None else gate_all.cuda()[:, 5:])
+            assert k.launch_count() - launches == 1
+        finally:
+            k.LATENT_PREFILL_MMA = True
+        assert rel_err(got, want) < (tol if dtype == torch.float32 else 4e-2), (mma, rel_err(got, want))   # bf16: K and V rounded after the expansion
     # single rows: the last row of each sequence, over splits of several sizes; what lies past the context is loud and must stay unseen
     cg[1, 150:, :] = 30.0
     cg[2, 111:, :] = 30.0
@@ -419,7 +440,7 @@ def test_each_mixer_alone(dtype, kind, cuts):
     assert_close(torch.cat(got), want, dtype, (kind, cuts))
 
 
-@pytest.mark.parametrize("cfg,seed", [(CFG_ODD, 11), (CFG_WIDE, 12)])
+@pytest.mark.parametrize("cfg,seed", [(CFG_ODD, 11), (CFG_WIDE, 12), (CFG_TILES, 13)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prompt_matches_oracle(cfg, seed, dtype):
     w = checkpoint(cfg, seed)
@@ -442,7 +463,7 @@ def test_layers_follow_the_oracle_one_by_one(cfg):
         assert rel_err(a, b) < 1e-5, f"layer {i}"
 
 
-@pytest.mark.parametrize("cfg", [CFG_ODD, CFG_WIDE])
+@pytest.mark.parametrize("cfg", [CFG_ODD, CFG_WIDE, CFG_TILES])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_decoding_token_by_token_equals_prefill(dtype, cfg):
     w = checkpoint(cfg, 31)
@@ -616,3 +637,32 @@ def test_trace_runner_end_to_end(tmp_path, dtype):
     for step, ref in want.items():
         assert got[step].shape == ref.shape
     assert_close(torch.cat([got[s] for s in want]), torch.cat(list(want.values())), torch.float32 if dtype == "float32" else torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prompts_on_the_tensor_cores_then_decoding(dtype):
+    """Two unequal prompts in one step (bf16: the tensor-core tiles for every latent layer), one longer than a query tile, then single
+    tokens for both while a third request arrives in portions."""
+    from lit_gpt_b200.generate.serve import Session
+
+    cfg = CFG_TILES
+    w = checkpoint(cfg, 61)
+    model = build(cfg, w, dtype)
+    session = Session(model, slots=2, max_seq_length=256)
+    a, b, c = tokens_for(cfg, 190, 62), tokens_for(cfg, 95, 63), tokens_for(cfg, 60, 64)
+    want = {r: O.forward(cfg, w, t) for r, t in (("a", a), ("b", b), ("c", c))}
+    out = session.step([("a", a[:160], [0, 63, 64, 127, 128, 159]), ("b", b[:65], [64])])
+    assert_close(out, torch.cat([want["a"][[0, 63, 64, 127, 128, 159]], want["b"][64:65]]), dtype, "prompts")
+    got = {"a": [], "b": [], "c": []}
+    for i in range(30):
+        entries = [("a", [a[160 + i]], [0]), ("b", [b[65 + i]], [0])]
+        if i % 10 == 5:                       # c's portions of 20 tokens ride along with the single-token steps
+            j = (i // 10) * 20
+            entries.append(("c", c[j : j + 20], None))
+        out = session.step(entries)
+        got["a"].append(out[0:1]); got["b"].append(out[1:2])
+        if len(entries) == 3:
+            got["c"].append(out[2:])
+    assert_close(torch.cat(got["a"]), want["a"][160:190], dtype, "a")
+    assert_close(torch.cat(got["b"]), want["b"][65:95], dtype, "b")
+    assert_close(torch.cat(got["c"]), want["c"], dtype, "c")
