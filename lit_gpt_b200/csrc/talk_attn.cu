@@ -34,6 +34,31 @@ __host__ __device__ inline size_t ta_smem_floats(int H, int bm, int dk, int dv) 
          (size_t)H * bm * dv + 8;
 }
 
+// four consecutive elements as floats (8- or 16-byte access; the caller has checked the alignment)
+__device__ __forceinline__ float4 ta_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ta_load4(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y));
+}
+
+// rows j0 .. j0 + 31 of a cache (row stride ld, `width` numbers from column col0) -> tile[32][pitch] as floats; rows from k_hi on and
+// the padding columns are zero.  A warp takes every eighth row, its lanes the columns (four at a time when `vec`).
+template <typename T>
+__device__ __forceinline__ void ta_load_tile(float* tile, const T* base, int64_t ld, int col0, int width, int pitch, int j0, int k_hi, bool vec) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int j = warp; j < kTaBN; j += kTaThreads / 32) {
+    float* dst = tile + j * pitch;
+    const bool ok = j0 + j < k_hi;
+    const T* src = base + (int64_t)(ok ? j0 + j : 0) * ld + col0;
+    if (vec) {
+      for (int d = lane * 4; d < pitch; d += 128)
+        *reinterpret_cast<float4*>(dst + d) = ok && d < width ? ta_load4(src + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      for (int d = lane; d < pitch; d += 32) dst[d] = ok && d < width ? load_as_float(src, d) : 0.f;
+    }
+  }
+}
+
 // grid (query tiles, splits, sequences)
 template <typename T, int BM>
 __global__ void __launch_bounds__(kTaThreads) talk_attn_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ kc, int64_t ldk,
@@ -68,6 +93,8 @@ __global__ void __launch_bounds__(kTaThreads) talk_attn_kernel(const T* __restri
   const int k_lo = split * per, k_hi = min(n_keys, k_lo + per);
   const T* kslot = kc + (int64_t)slot * max_seq * ldk;
   const T* vslot = vc + (int64_t)slot * max_seq * ldv;
+  const bool kvec = dk % 4 == 0 && ldk % 4 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;
+  const bool vvec = dv % 4 == 0 && ldv % 4 == 0 && (reinterpret_cast<uintptr_t>(vc) & 15) == 0;
 
   for (int idx = tid; idx < H * BM * dkp; idx += kTaThreads) {
     const int hh = idx / (BM * dkp), rem = idx - hh * BM * dkp, i = rem / dkp, d = rem - i * dkp;
@@ -83,12 +110,7 @@ __global__ void __launch_bounds__(kTaThreads) talk_attn_kernel(const T* __restri
     // raw scores, one group of heads after the other
     for (int g = 0; g < G; ++g) {
       __syncthreads();                                 // the tile buffer is free (and Q is complete on the first pass)
-      for (int idx = tid; idx < kTaBN * dkp; idx += kTaThreads) {
-        const int j = idx / dkp, d = idx - j * dkp;
-        float val = 0.f;
-        if (j0 + j < k_hi && d < dk) val = load_as_float(kslot, (int64_t)(j0 + j) * ldk + (int64_t)g * dk + d);
-        KV[idx] = val;
-      }
+      ta_load_tile(KV, kslot, ldk, g * dk, dk, dkp, j0, k_hi, kvec);
       __syncthreads();
       const float* krow = KV + lane * dkp;
       for (int pair = warp; pair < per_g * BM; pair += kTaThreads / 32) {   // a warp: one (head, row), its lanes the 32 keys
@@ -130,13 +152,33 @@ __global__ void __launch_bounds__(kTaThreads) talk_attn_kernel(const T* __restri
     // value sums, one group of heads after the other
     for (int g = 0; g < G; ++g) {
       __syncthreads();                                 // the tile buffer is free; probabilities and factors are complete
-      for (int idx = tid; idx < kTaBN * dvp; idx += kTaThreads) {
-        const int j = idx / dvp, c = idx - j * dvp;
-        float val = 0.f;
-        if (j0 + j < k_hi && c < dv) val = load_as_float(vslot, (int64_t)(j0 + j) * ldv + (int64_t)g * dv + c);
-        KV[idx] = val;
-      }
+      ta_load_tile(KV, vslot, ldv, g * dv, dv, dvp, j0, k_hi, vvec);
       __syncthreads();
+      if (vvec) {   // four neighbouring value columns per thread: one 16-byte read of V per key serves 4 x BM sums
+        for (int item = tid; item < per_g * (dv / 4); item += kTaThreads) {
+          const int hq = g * per_g + item / (dv / 4), c = (item % (dv / 4)) * 4;
+          float acc[BM][4];
+#pragma unroll
+          for (int i = 0; i < BM; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+          const float* pr = P + (size_t)hq * TS;
+#pragma unroll 4
+          for (int j = 0; j < kTaBN; ++j) {
+            const float4 v = *reinterpret_cast<const float4*>(KV + j * dvp + c);
+#pragma unroll
+            for (int i = 0; i < BM; ++i) {
+              const float p = pr[i * kTaBN + j];
+              acc[i][0] = fmaf(p, v.x, acc[i][0]); acc[i][1] = fmaf(p, v.y, acc[i][1]);
+              acc[i][2] = fmaf(p, v.z, acc[i][2]); acc[i][3] = fmaf(p, v.w, acc[i][3]);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < BM; ++i) {
+            float* o = O + ((size_t)hq * BM + i) * dv + c;
+            const float a = Al[hq * BM + i];
+            o[0] = o[0] * a + acc[i][0]; o[1] = o[1] * a + acc[i][1]; o[2] = o[2] * a + acc[i][2]; o[3] = o[3] * a + acc[i][3];
+          }
+        }
+      } else
       for (int item = tid; item < per_g * dv; item += kTaThreads) {
         const int hq = g * per_g + item / dv, c = item % dv;
         float acc[BM];
