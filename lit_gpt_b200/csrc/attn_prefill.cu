@@ -44,9 +44,16 @@ struct PfView {
   const __nv_bfloat16* gate;
   int64_t gate_r;
   int gate_mode;
+  // ragged only, kernels instantiated with MODE 1 or 2: the score planes sbuf[h * s_h + packed query row * s_r + key position] (fp32,
+  // already times scale * log2(e)).  MODE 1 writes the raw scores of every tile it visits there and stops; MODE 2 reads them back
+  // (after another kernel has worked on them) instead of multiplying q and k.  kv_slot_rows > 0: seqs[b].w is a cache slot and
+  // position 0 of the sequence is row w * kv_slot_rows of k / v.
+  float* sbuf;
+  int64_t s_h, s_r;
+  int64_t kv_slot_rows;
 };
 
-template <int HS, typename PosT, int HK2 = 0>
+template <int HS, typename PosT, int HK2 = 0, int MODE = 0>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                     const PosT* __restrict__ pos, __nv_bfloat16* __restrict__ y, int T, int n_head, int n_groups, int max_seq,
@@ -77,7 +84,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     pos0 = sq.z;
     max_seq = sq.z + sq.y;
     qrow0 = sq.x;
-    kvrow0 = vw.kv_first_row ? sq.x : sq.w;
+    kvrow0 = vw.kv_first_row ? sq.x : (vw.kv_slot_rows > 0 ? (int64_t)sq.w * vw.kv_slot_rows : sq.w);
     if (r0 >= T) return;
   }
 
@@ -100,6 +107,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   if (lane == 0) s_maxpos[warp] = wl;
 
   // Q tile -> shared (rows past T are zero-filled)
+  if constexpr (MODE != 2)
   for (int i = tid; i < kPfBM * CH; i += kPfThreads) {
     const int r = i / CH, c = i % CH;
     const bool ok = r0 + r < T;
@@ -130,8 +138,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const int r = i / CH, c = i % CH;
       const bool ok = j0 + r <= cta_lim;
       const int64_t row = ok ? j0 + r : 0;
-      pf_cp16(pf_smem(sK) + buf * KB + sw<HS>(r, c), kg + row * vw.k_r + c * 8, ok);
-      pf_cp16(pf_smem(sV) + buf * KB + sw<HS>(r, c), vg + row * vw.v_r + c * 8, ok);
+      if constexpr (MODE != 2) pf_cp16(pf_smem(sK) + buf * KB + sw<HS>(r, c), kg + row * vw.k_r + c * 8, ok);
+      if constexpr (MODE != 1) pf_cp16(pf_smem(sV) + buf * KB + sw<HS>(r, c), vg + row * vw.v_r + c * 8, ok);
     }
     if constexpr (HK2 > 0) {
       for (int i = tid; i < kPfBN * CH2; i += kPfThreads) {
@@ -152,10 +160,14 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   // Q fragments stay in registers for the whole key loop
   pf_wait<1>();
   __syncthreads();
-  uint32_t qf[HS / 16][4];
+  uint32_t qf[MODE == 2 ? 1 : HS / 16][4];
+  if constexpr (MODE != 2) {
 #pragma unroll
-  for (int ks = 0; ks < HS / 16; ++ks)
-    ldsm_x4(qf[ks], pf_smem(sQ) + sw<HS>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+    for (int ks = 0; ks < HS / 16; ++ks)
+      ldsm_x4(qf[ks], pf_smem(sQ) + sw<HS>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+  }
+  float* const planeA = MODE != 0 ? vw.sbuf + (int64_t)h * vw.s_h + (qrow0 + rowA) * vw.s_r : nullptr;   // this thread's two rows of the score plane
+  float* const planeB = MODE != 0 ? planeA + 8 * vw.s_r : nullptr;
   uint32_t qf2[HK2 > 0 ? HK2 / 16 : 1][4];
   if constexpr (HK2 > 0) {
 #pragma unroll
@@ -174,6 +186,14 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
       for (int i = 0; i < kPfBN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       const uint32_t kb = pf_smem(sK) + buf * KB, vb = pf_smem(sV) + buf * KB;
+      if constexpr (MODE == 2) {   // the scores were computed (and worked on) before: fetch this thread's share of the tile
+#pragma unroll
+        for (int i = 0; i < kPfBN / 8; ++i) {
+          const int j = j0 + i * 8 + 2 * tq;
+          if (rowA < T) { const float2 v = *reinterpret_cast<const float2*>(planeA + j); s[i][0] = v.x; s[i][1] = v.y; }
+          if (rowB < T) { const float2 v = *reinterpret_cast<const float2*>(planeB + j); s[i][2] = v.x; s[i][3] = v.y; }
+        }
+      } else {
 #pragma unroll
       for (int ks = 0; ks < HS / 16; ++ks) {
 #pragma unroll
@@ -184,6 +204,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           pf_mma(s[2 * np + 1], qf[ks], kf[2], kf[3]);
         }
       }
+      }
+      if constexpr (MODE == 1) {   // leave the raw scores (times scale * log2 e) in the plane; the rest happens in later launches
+#pragma unroll
+        for (int i = 0; i < kPfBN / 8; ++i) {
+          const int j = j0 + i * 8 + 2 * tq;
+          if (rowA < T) *reinterpret_cast<float2*>(planeA + j) = make_float2(s[i][0] * scale_log2, s[i][1] * scale_log2);
+          if (rowB < T) *reinterpret_cast<float2*>(planeB + j) = make_float2(s[i][2] * scale_log2, s[i][3] * scale_log2);
+        }
+      } else {
       if constexpr (HK2 > 0) {   // the shared key part's share of the scores
         const uint32_t kb2 = pf_smem(sK2) + buf * KB2;
 #pragma unroll
@@ -243,10 +272,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           pf_mma(o_acc[2 * dp + 1], pfr[ks], vf[2], vf[3]);
         }
       }
+      }   // MODE != 1
     }
     __syncthreads();   // the buffer just read is refilled by the next iteration's prefetch
   }
 
+  if constexpr (MODE == 1) return;
   lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
   lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
   float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
@@ -283,30 +314,96 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 }
 
-template <int HS, typename PosT, int HK2 = 0>
+template <int HS, typename PosT, int HK2 = 0, int MODE = 0>
 cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const void* pos, void* y, int B, int T, int H, int G, int max_seq,
                            float scale, cudaStream_t st, const PfView* view = nullptr) {
   // default: q (B, H, T, HS), caches (B, G, max_seq, HS), y (B, T, H * HS)
   const PfView vw = view ? *view
                          : PfView{(int64_t)H * T * HS, (int64_t)T * HS, HS, (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS,
                                   (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr, 0, nullptr, 0,
-                                  nullptr, 0, nullptr, 0, 0};
+                                  nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0};
   const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2 + (size_t)(kPfBM + 2 * kPfBN) * HK2 * 2;
   static PerDeviceOnce once;
   if (once.need()) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HS, PosT, HK2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HS, PosT, HK2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     once.done();
   }
   dim3 grid((T + kPfBM - 1) / kPfBM, H, B);
-  return launch(attn_prefill_kernel<HS, PosT, HK2>, grid, dim3(kPfThreads), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
+  return launch(attn_prefill_kernel<HS, PosT, HK2, MODE>, grid, dim3(kPfThreads), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
                 (const __nv_bfloat16*)vc, (const PosT*)pos, (__nv_bfloat16*)y, T, H, G, max_seq, scale * 1.4426950408889634f, vw);
+}
+
+// s'[h] = sum_g talk[h, g] s[g] at every (query row, key position <= the row's position) of the score planes, in place: a thread
+// owns one (row, key) pair, holds its HT >= n_head scores in registers, and reads the mixing matrix from shared memory.
+template <int HT>
+__global__ void __launch_bounds__(256) mix_scores_kernel(float* __restrict__ sbuf, int64_t s_h, int64_t s_r, const __nv_bfloat16* __restrict__ talk,
+                                                          const int* __restrict__ row_pos, int n_head) {
+  __shared__ __align__(16) float tm[HT * HT];
+  griddep_launch();
+  griddep_wait();
+  for (int i = threadIdx.x; i < HT * HT; i += 256) {
+    const int h = i / HT, g = i % HT;
+    tm[i] = h < n_head && g < n_head ? __bfloat162float(talk[h * n_head + g]) : 0.f;
+  }
+  __syncthreads();
+  const int64_t row = blockIdx.x;
+  const int j = (int)blockIdx.y * 256 + threadIdx.x;
+  if (j > row_pos[row]) return;
+  float* p = sbuf + row * s_r + j;
+  float in[HT];
+#pragma unroll
+  for (int g = 0; g < HT; ++g) in[g] = g < n_head ? p[(int64_t)g * s_h] : 0.f;
+  for (int h = 0; h < n_head; ++h) {
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < HT; g += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(tm + h * HT + g);
+      acc = fmaf(t.x, in[g], acc); acc = fmaf(t.y, in[g + 1], acc); acc = fmaf(t.z, in[g + 2], acc); acc = fmaf(t.w, in[g + 3], acc);
+    }
+    p[(int64_t)h * s_h] = acc;
+  }
 }
 
 }  // namespace
 }  // namespace b200
 
 using namespace b200;
+
+// Causal attention over cache rows with the heads' scores mixed before the softmax, for bf16 prompts on the tensor-core tiles, as
+// three launches over fp32 score planes sbuf (n_head, rows, s_ld): (1) raw scores of every visible tile, (2) the mixing, in place,
+// (3) softmax with the sink and the value product reading the mixed scores back.  seqs[b] = {first row, rows, first position, cache
+// slot}; k_cache / v_cache rows of a slot are max_seq apart; row_pos[i] = position of packed row i; talk NULL: no mixing.
+extern "C" int b200_attn_prefill_mixed(const void* q, int64_t ldq, const void* k_cache, int64_t ldk, const void* v_cache, int64_t ldv,
+                                       const int32_t* seqs, int n_seqs, int max_q_len, int max_seq, const int32_t* row_pos, int64_t rows,
+                                       const void* talk, const void* sink, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size,
+                                       float scale, float* sbuf, int64_t s_ld, b200_stream_t stream) {
+  B200_CHECK_ARG(q && k_cache && v_cache && seqs && row_pos && y && sbuf, "b200_attn_prefill_mixed: null pointer");
+  B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && rows > 0 && rows <= 0x7fffffff && n_head > 0 && n_head <= 64 && n_kv_head > 0 &&
+                     n_head % n_kv_head == 0 && max_seq > 0, "b200_attn_prefill_mixed: bad shape (at most 64 heads)");
+  B200_CHECK_ARG(head_size == 64 || head_size == 128, "b200_attn_prefill_mixed: head_size must be 64 or 128 (got %d)", head_size);
+  B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0 && (s_ld & 63) == 0, "b200_attn_prefill_mixed: leading dimensions must be multiples of 8 elements, the planes' of 64");
+  B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                   reinterpret_cast<uintptr_t>(seqs) | reinterpret_cast<uintptr_t>(sbuf)) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 3) == 0,
+                 "b200_attn_prefill_mixed: operands must be 16-byte aligned");
+  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0,
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 0, nullptr, 0, nullptr, 0, 0, sbuf, rows * s_ld, s_ld, max_seq};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 0, 1>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
+  else B200_CUDA((launch_prefill<64, int32_t, 0, 1>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
+  if (talk) {
+    const dim3 grid((unsigned)rows, (unsigned)((s_ld + 255) / 256));
+    const __nv_bfloat16* tk = reinterpret_cast<const __nv_bfloat16*>(talk);
+    if (n_head <= 8) B200_CUDA(launch(mix_scores_kernel<8>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
+    else if (n_head <= 16) B200_CUDA(launch(mix_scores_kernel<16>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
+    else if (n_head <= 32) B200_CUDA(launch(mix_scores_kernel<32>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
+    else B200_CUDA(launch(mix_scores_kernel<64>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
+  }
+  // the planes are in the log2 domain already: the last pass scales by 1
+  if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 0, 2>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, 0.6931471805599453f, st, &vw)));
+  else B200_CUDA((launch_prefill<64, int32_t, 0, 2>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, 0.6931471805599453f, st, &vw)));
+  return B200_OK;
+}
 
 extern "C" int b200_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const void* pos, int pos_is_int64, void* y,
                                  int batch, int T, int n_head, int n_groups, int head_size, int max_seq, float scale,
@@ -339,7 +436,7 @@ extern "C" int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_ragged: operands must be 16-byte aligned");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0, nullptr, 0,
-                  nullptr, 0, nullptr, 0, 0};
+                  nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
@@ -359,7 +456,7 @@ extern "C" int b200_attn_prefill_window(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_window: operands must be 16-byte aligned");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), window,
-                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, nullptr, 0, 0};
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
@@ -384,7 +481,7 @@ extern "C" int b200_attn_prefill_shared(const void* q, int64_t ldq, const void* 
                  "b200_attn_prefill_shared: operands must be 16-byte aligned");
   const PfView vw{0, head_size + dk2, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0,
                   reinterpret_cast<const __nv_bfloat16*>(sink), 0, reinterpret_cast<const __nv_bfloat16*>(k2), ldk2,
-                  reinterpret_cast<const __nv_bfloat16*>(gate), ldg, gate_mode};
+                  reinterpret_cast<const __nv_bfloat16*>(gate), ldg, gate_mode, nullptr, 0, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128 && dk2 == 64) B200_CUDA((launch_prefill<128, int32_t, 64>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   else if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 128>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));

@@ -383,6 +383,24 @@ def test_mixed_score_attention_kernel(dtype, sizes):
     seqs = torch.tensor([(0, 101, 0, 2), (101, 50, 37, 0)], dtype=torch.int32, device="cuda")
     got = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, talk=talk.cuda(), sink=sink.cuda())
     assert rel_err(got, want) < tol, rel_err(got, want)
+    if dtype == torch.bfloat16 and dk == dv and dk in (64, 128):
+        # the same prompts on the tensor-core tiles: raw scores into fp32 planes, mixing in place, softmax and values from the planes
+        rp = torch.tensor(list(range(101)) + list(range(37, 87)), dtype=torch.int32, device="cuda")
+        for tk in (talk.cuda(), None):
+            launches = k.launch_count()
+            got = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, talk=tk, sink=sink.cuda(), row_pos=rp,
+                              context=101)
+            assert k.launch_count() - launches == (3 if tk is not None else 2)
+            if tk is not None:
+                assert rel_err(got, want) < 3e-2, rel_err(got, want)
+            else:
+                k.TALK_PREFILL_MMA = False
+                try:
+                    other = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, sink=sink.cuda(), row_pos=rp,
+                                        context=101)
+                finally:
+                    k.TALK_PREFILL_MMA = True
+                assert rel_err(got, other) < 3e-2
     last = [100, 150]
     seqs1 = torch.tensor([(0, 1, 100, 2), (1, 1, 86, 0)], dtype=torch.int32, device="cuda")
     for splits in (1, 2, 4, 9):
