@@ -342,6 +342,7 @@ __global__ void __launch_bounds__(256) mix_scores_kernel(float* __restrict__ sbu
   __shared__ __align__(16) float tm[HT * HT];
   griddep_launch();
   griddep_wait();
+  if ((int)blockIdx.y * 256 > row_pos[blockIdx.x]) return;   // the whole block lies beyond what the row sees
   for (int i = threadIdx.x; i < HT * HT; i += 256) {
     const int h = i / HT, g = i % HT;
     tm[i] = h < n_head && g < n_head ? __bfloat162float(talk[h * n_head + g]) : 0.f;

@@ -213,33 +213,48 @@ __global__ void __launch_bounds__(kTaThreads) talk_attn_kernel(const T* __restri
   }
 }
 
-// one warp per (row, head): the splits' sums brought to one maximum, the sink joined to the denominator
+// one CTA per (row, head): the splits' sums brought to one maximum, the sink joined to the denominator.  The splits' weights are
+// worked out once in shared memory; then a thread owns output columns and walks the splits with independent loads.
+constexpr int kTmThreads = 128;
+
 template <typename T>
-__global__ void __launch_bounds__(128) talk_attn_merge_kernel(const float* __restrict__ ws, const T* __restrict__ sink, T* __restrict__ out, int64_t ldo,
-                                                               int64_t rows, int H, int dv, int n_split) {
+__global__ void __launch_bounds__(kTmThreads) talk_attn_merge_kernel(const float* __restrict__ ws, const T* __restrict__ sink, T* __restrict__ out,
+                                                                      int64_t ldo, int H, int dv, int n_split) {
+  extern __shared__ __align__(16) float tm_smem[];   // [n_split] weights
+  __shared__ float s_red[kTmThreads / 32];
+  __shared__ float s_val[2];
   griddep_launch();
   griddep_wait();
-  const int lane = threadIdx.x & 31;
-  const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= rows * H) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t item = blockIdx.x;
   const int64_t row = item / H;
   const int h = (int)(item - row * H);
   const float* src = ws + item * n_split * (dv + 2);
   const float sink_l = sink ? load_as_float(sink, h) * 1.4426950408889634f : -INFINITY;
   float mx = sink_l;
-  for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, src[(int64_t)s * (dv + 2) + dv]);
-  float tot = sink ? exp2f(sink_l - mx) : 0.f;
-  for (int s = 0; s < n_split; ++s) {
+  for (int s = tid; s < n_split; s += kTmThreads) mx = fmaxf(mx, src[(int64_t)s * (dv + 2) + dv]);
+  mx = warp_max(mx);
+  if (lane == 0) s_red[warp] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));      // finite: some split saw a key
+  float part = 0.f;
+  for (int s = tid; s < n_split; s += kTmThreads) {
     const float m = src[(int64_t)s * (dv + 2) + dv];
-    if (m != -INFINITY) tot = fmaf(exp2f(m - mx), src[(int64_t)s * (dv + 2) + dv + 1], tot);
+    const float w = m == -INFINITY ? 0.f : exp2f(m - mx);
+    tm_smem[s] = w;
+    part = fmaf(w, src[(int64_t)s * (dv + 2) + dv + 1], part);
   }
-  const float inv = 1.0f / tot;
-  for (int c = lane; c < dv; c += 32) {
+  part = warp_sum(part);
+  __syncthreads();                                                       // s_red has been read by everyone
+  if (lane == 0) s_red[warp] = part;
+  __syncthreads();
+  if (tid == 0) s_val[0] = 1.0f / (s_red[0] + s_red[1] + s_red[2] + s_red[3] + (sink ? exp2f(sink_l - mx) : 0.f));
+  __syncthreads();
+  const float inv = s_val[0];
+  for (int c = tid; c < dv; c += kTmThreads) {
     float acc = 0.f;
-    for (int s = 0; s < n_split; ++s) {
-      const float m = src[(int64_t)s * (dv + 2) + dv];
-      if (m != -INFINITY) acc = fmaf(exp2f(m - mx), src[(int64_t)s * (dv + 2) + c], acc);
-    }
+#pragma unroll 4
+    for (int s = 0; s < n_split; ++s) acc = fmaf(tm_smem[s], src[(int64_t)s * (dv + 2) + c], acc);
     store_from_float(out, row * ldo + (int64_t)h * dv + c, acc * inv);
   }
 }
@@ -272,8 +287,8 @@ int talk_run(const b200_talk_attn_args* a, cudaStream_t st) {
   int rc = bm == 4 ? talk_launch<T, 4>(a, st, smem) : bm == 2 ? talk_launch<T, 2>(a, st, smem) : talk_launch<T, 1>(a, st, smem);
   if (rc != B200_OK) return rc;
   const int64_t items = a->rows * a->n_head;
-  B200_CUDA(launch(talk_attn_merge_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, st, (const float*)a->workspace, (const T*)a->sink, (T*)a->out,
-                   a->ldo, a->rows, a->n_head, a->dv, a->n_split));
+  B200_CUDA(launch(talk_attn_merge_kernel<T>, dim3((unsigned)items), dim3(kTmThreads), (size_t)a->n_split * sizeof(float), st, (const float*)a->workspace,
+                   (const T*)a->sink, (T*)a->out, a->ldo, a->n_head, a->dv, a->n_split));
   return B200_OK;
 }
 
