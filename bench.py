@@ -866,8 +866,7 @@ def run_fizadra_compare(args) -> None:
             # prompt attention with mixed scores, over the cache rows
             ta = fiz.blocks[2].mixer
             kc, vc = torch.randn(T, G * hs, device=dev, dtype=bf), torch.randn(T, G * hs, device=dev, dtype=bf)
-            posT = torch.arange(T, device=dev, dtype=torch.int32)
-            ms = _timed(lambda: K.talk_attn(qp, kc, vc, seqs, T, H, G, hs, hs, T, hs ** -0.5, 1, talk=ta.talk, sink=ta.sink, row_pos=posT, context=T), iters, flush)
+            ms = _timed(lambda: K.talk_attn(qp, kc, vc, seqs, T, H, G, hs, hs, T, hs ** -0.5, 1, talk=ta.talk, sink=ta.sink, context=T), iters, flush)
             kern["prefill_mixed_score_attention_fizadra"] = {"ms": ms, "frac_of_measured_bf16": (4.0 * H * hs + 2.0 * H * H) * pairs / (ms * 1e-3) / tf,
                                                              "plane_bytes_moved": 4.0 * H * pairs * 4, "frac_of_measured_hbm_for_planes": 4.0 * H * pairs * 4 / (ms * 1e-3) / hbm}
             ms = _timed(lambda: K.talk_attn(qp, kc, vc, seqs, T, H, G, hs, hs, T, hs ** -0.5, 1, talk=ta.talk, sink=ta.sink), max(2, iters // 4), flush)

@@ -595,13 +595,13 @@ typedef struct b200_talk_attn_args {
   void* workspace; size_t workspace_bytes;
 } b200_talk_attn_args;
 /* The same attention for bf16 prompts with dk = dv = head_size in {64, 128} and at most 64 heads, on the tensor-core prefill tiles, as
- * three launches over fp32 score planes sbuf (n_head, rows, s_ld), s_ld a multiple of 64 not below the longest context: raw scores,
- * the mixing in place, softmax with the sink and the value product.  row_pos[i]: position of packed row i.  Operands 16-byte aligned,
- * leading dimensions multiples of 8. */
+ * three launches over fp32 score planes: raw scores, the mixing in place, softmax with the sink and the value product.  sbuf holds
+ * n_head planes of b200_attn_prefill_mixed_plane_floats(n_seqs, max_q_len, s_ld) floats each; s_ld is a multiple of 64 not below the
+ * longest context.  Operands 16-byte aligned, leading dimensions multiples of 8. */
+size_t b200_attn_prefill_mixed_plane_floats(int n_seqs, int max_q_len, int64_t s_ld);
 int b200_attn_prefill_mixed(const void* q, int64_t ldq, const void* k_cache, int64_t ldk, const void* v_cache, int64_t ldv, const int32_t* seqs,
-                            int n_seqs, int max_q_len, int max_seq, const int32_t* row_pos, int64_t rows, const void* talk, const void* sink,
-                            void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale, float* sbuf, int64_t s_ld,
-                            b200_stream_t stream);
+                            int n_seqs, int max_q_len, int max_seq, const void* talk, const void* sink, void* y, int64_t ldy, int n_head,
+                            int n_kv_head, int head_size, float scale, float* sbuf, int64_t s_ld, b200_stream_t stream);
 size_t b200_talk_attn_workspace_bytes(int64_t rows, int n_head, int dv, int n_split);
 int b200_talk_attn(const b200_talk_attn_args* args, b200_stream_t stream);
 

@@ -182,8 +182,9 @@ _CORE_SIGNATURES = {
     "b200_window_attn_tune": (c_int, [c_int]),
     "b200_depth_residual": (c_int, [ctypes.POINTER(DepthResidualArgs), c_void_p]),
     "b200_head_rope": (c_int, [ctypes.POINTER(HeadRopeSeg), c_int, c_void_p, c_int64, c_float, c_int, c_void_p]),
-    "b200_attn_prefill_mixed": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_int64,
-                                        c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p, c_int64, c_void_p]),
+    "b200_attn_prefill_mixed_plane_floats": (c_size_t, [c_int, c_int, c_int64]),
+    "b200_attn_prefill_mixed": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p, c_int64, c_void_p]),
     "b200_talk_attn_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int]),
     "b200_talk_attn": (c_int, [ctypes.POINTER(TalkAttnArgs), c_void_p]),
     "b200_attn_prefill_window": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,

@@ -44,12 +44,15 @@ struct PfView {
   const __nv_bfloat16* gate;
   int64_t gate_r;
   int gate_mode;
-  // ragged only, kernels instantiated with MODE 1 or 2: the score planes sbuf[h * s_h + packed query row * s_r + key position] (fp32,
-  // already times scale * log2(e)).  MODE 1 writes the raw scores of every tile it visits there and stops; MODE 2 reads them back
-  // (after another kernel has worked on them) instead of multiplying q and k.  kv_slot_rows > 0: seqs[b].w is a cache slot and
-  // position 0 of the sequence is row w * kv_slot_rows of k / v.
+  // ragged only, kernels instantiated with MODE 1 or 2: fp32 score planes, one per head (s_h floats apart), already times scale *
+  // log2(e).  A plane is a run of 128 x 64 tiles, tile (sequence b, query tile mt, key tile kt) at ((b * s_qt + mt) * s_kt + kt) * 8192,
+  // each stored in the accumulator layout of the warp that owns it: [warp][8-key step][lane][4], so a lane's four numbers are one
+  // 16-byte access and a warp's access is contiguous.  MODE 1 writes the raw scores of every tile it visits and stops; MODE 2 reads
+  // them back (after another kernel has worked on them) instead of multiplying q and k.  kv_slot_rows > 0: seqs[b].w is a cache slot
+  // and position 0 of the sequence is row w * kv_slot_rows of k / v.
   float* sbuf;
-  int64_t s_h, s_r;
+  int64_t s_h;
+  int s_qt, s_kt;
   int64_t kv_slot_rows;
 };
 
@@ -166,8 +169,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int ks = 0; ks < HS / 16; ++ks)
       ldsm_x4(qf[ks], pf_smem(sQ) + sw<HS>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
   }
-  float* const planeA = MODE != 0 ? vw.sbuf + (int64_t)h * vw.s_h + (qrow0 + rowA) * vw.s_r : nullptr;   // this thread's two rows of the score plane
-  float* const planeB = MODE != 0 ? planeA + 8 * vw.s_r : nullptr;
+  // this lane's place in the first key tile of its query tile's run of the score plane
+  float* const plane = MODE != 0 ? vw.sbuf + (int64_t)h * vw.s_h + ((int64_t)b * vw.s_qt + mt) * vw.s_kt * (kPfBM * kPfBN) + (warp * 256 + lane) * 4 : nullptr;
   uint32_t qf2[HK2 > 0 ? HK2 / 16 : 1][4];
   if constexpr (HK2 > 0) {
 #pragma unroll
@@ -187,11 +190,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       for (int i = 0; i < kPfBN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       const uint32_t kb = pf_smem(sK) + buf * KB, vb = pf_smem(sV) + buf * KB;
       if constexpr (MODE == 2) {   // the scores were computed (and worked on) before: fetch this thread's share of the tile
+        const float* tp = plane + (int64_t)tile * (kPfBM * kPfBN);
 #pragma unroll
         for (int i = 0; i < kPfBN / 8; ++i) {
-          const int j = j0 + i * 8 + 2 * tq;
-          if (rowA < T) { const float2 v = *reinterpret_cast<const float2*>(planeA + j); s[i][0] = v.x; s[i][1] = v.y; }
-          if (rowB < T) { const float2 v = *reinterpret_cast<const float2*>(planeB + j); s[i][2] = v.x; s[i][3] = v.y; }
+          const float4 v = *reinterpret_cast<const float4*>(tp + i * 128);
+          s[i][0] = v.x; s[i][1] = v.y; s[i][2] = v.z; s[i][3] = v.w;
         }
       } else {
 #pragma unroll
@@ -206,12 +209,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       }
       }
       if constexpr (MODE == 1) {   // leave the raw scores (times scale * log2 e) in the plane; the rest happens in later launches
+        float* tp = plane + (int64_t)tile * (kPfBM * kPfBN);
 #pragma unroll
-        for (int i = 0; i < kPfBN / 8; ++i) {
-          const int j = j0 + i * 8 + 2 * tq;
-          if (rowA < T) *reinterpret_cast<float2*>(planeA + j) = make_float2(s[i][0] * scale_log2, s[i][1] * scale_log2);
-          if (rowB < T) *reinterpret_cast<float2*>(planeB + j) = make_float2(s[i][2] * scale_log2, s[i][3] * scale_log2);
-        }
+        for (int i = 0; i < kPfBN / 8; ++i)
+          *reinterpret_cast<float4*>(tp + i * 128) = make_float4(s[i][0] * scale_log2, s[i][1] * scale_log2, s[i][2] * scale_log2, s[i][3] * scale_log2);
       } else {
       if constexpr (HK2 > 0) {   // the shared key part's share of the scores
         const uint32_t kb2 = pf_smem(sK2) + buf * KB2;
@@ -321,7 +322,7 @@ cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const 
   const PfView vw = view ? *view
                          : PfView{(int64_t)H * T * HS, (int64_t)T * HS, HS, (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS,
                                   (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr, 0, nullptr, 0,
-                                  nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0};
+                                  nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0, 0};
   const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2 + (size_t)(kPfBM + 2 * kPfBN) * HK2 * 2;
   static PerDeviceOnce once;
   if (once.need()) {
@@ -334,35 +335,41 @@ cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const 
                 (const __nv_bfloat16*)vc, (const PosT*)pos, (__nv_bfloat16*)y, T, H, G, max_seq, scale * 1.4426950408889634f, vw);
 }
 
-// s'[h] = sum_g talk[h, g] s[g] at every (query row, key position <= the row's position) of the score planes, in place: a thread
-// owns one (row, key) pair, holds its HT >= n_head scores in registers, and reads the mixing matrix from shared memory.
+// s'[h] = sum_g talk[h, g] s[g] at every element of the score planes' tiles that the first pass wrote, in place.  The planes share
+// one layout, so the same offset in every plane is the same (query row, key) pair: a thread owns an offset, holds its HT >= n_head
+// scores in registers and reads the mixing matrix from shared memory.  grid (tiles, 8): a block takes the 16 rows x 64 keys of one warp
+// of the tile kernels and leaves at once when that warp skipped the tile (its rows lie before the tile's keys, or past the sequence).
 template <int HT>
-__global__ void __launch_bounds__(256) mix_scores_kernel(float* __restrict__ sbuf, int64_t s_h, int64_t s_r, const __nv_bfloat16* __restrict__ talk,
-                                                          const int* __restrict__ row_pos, int n_head) {
+__global__ void __launch_bounds__(256) mix_scores_kernel(float* __restrict__ sbuf, int64_t s_h, int s_qt, int s_kt, const __nv_bfloat16* __restrict__ talk,
+                                                          const int4* __restrict__ seqs, int n_head) {
   __shared__ __align__(16) float tm[HT * HT];
   griddep_launch();
   griddep_wait();
-  if ((int)blockIdx.y * 256 > row_pos[blockIdx.x]) return;   // the whole block lies beyond what the row sees
+  const int kt = (int)blockIdx.x % s_kt, mt = ((int)blockIdx.x / s_kt) % s_qt, b = (int)blockIdx.x / (s_kt * s_qt), w = blockIdx.y;
+  const int4 sq = seqs[b];
+  const int first = mt * kPfBM + w * 16;                       // the block's first row in its sequence
+  if (first >= sq.y) return;
+  if (kt * kPfBN > sq.z + min(first + 15, sq.y - 1)) return;   // every key of the tile lies beyond what these rows see
   for (int i = threadIdx.x; i < HT * HT; i += 256) {
     const int h = i / HT, g = i % HT;
     tm[i] = h < n_head && g < n_head ? __bfloat162float(talk[h * n_head + g]) : 0.f;
   }
   __syncthreads();
-  const int64_t row = blockIdx.x;
-  const int j = (int)blockIdx.y * 256 + threadIdx.x;
-  if (j > row_pos[row]) return;
-  float* p = sbuf + row * s_r + j;
-  float in[HT];
+  float* base = sbuf + (int64_t)blockIdx.x * (kPfBM * kPfBN) + w * 1024 + threadIdx.x;
+  for (int k = 0; k < 4; ++k) {
+    float* p = base + k * 256;
+    float in[HT];
 #pragma unroll
-  for (int g = 0; g < HT; ++g) in[g] = g < n_head ? p[(int64_t)g * s_h] : 0.f;
-  for (int h = 0; h < n_head; ++h) {
-    float acc = 0.f;
+    for (int g = 0; g < HT; ++g) in[g] = g < n_head ? p[(int64_t)g * s_h] : 0.f;
+    for (int h = 0; h < n_head; ++h) {
+      float acc = 0.f;
 #pragma unroll
-    for (int g = 0; g < HT; g += 4) {
-      const float4 t = *reinterpret_cast<const float4*>(tm + h * HT + g);
-      acc = fmaf(t.x, in[g], acc); acc = fmaf(t.y, in[g + 1], acc); acc = fmaf(t.z, in[g + 2], acc); acc = fmaf(t.w, in[g + 3], acc);
+      for (int g = 0; g < HT; g += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(tm + h * HT + g);
+        acc = fmaf(t.x, in[g], acc); acc = fmaf(t.y, in[g + 1], acc); acc = fmaf(t.z, in[g + 2], acc); acc = fmaf(t.w, in[g + 3], acc);
+      }
+      p[(int64_t)h * s_h] = acc;
     }
-    p[(int64_t)h * s_h] = acc;
   }
 }
 
@@ -372,33 +379,42 @@ __global__ void __launch_bounds__(256) mix_scores_kernel(float* __restrict__ sbu
 using namespace b200;
 
 // Causal attention over cache rows with the heads' scores mixed before the softmax, for bf16 prompts on the tensor-core tiles, as
-// three launches over fp32 score planes sbuf (n_head, rows, s_ld): (1) raw scores of every visible tile, (2) the mixing, in place,
-// (3) softmax with the sink and the value product reading the mixed scores back.  seqs[b] = {first row, rows, first position, cache
-// slot}; k_cache / v_cache rows of a slot are max_seq apart; row_pos[i] = position of packed row i; talk NULL: no mixing.
+// three launches over fp32 score planes: (1) raw scores of every visible tile, (2) the mixing, in place, (3) softmax with the sink and
+// the value product reading the mixed scores back.  sbuf holds n_head planes of n_seqs * ceil(max_q_len / 128) * (s_ld / 64) tiles of
+// 8192 floats.  seqs[b] = {first row, rows, first position, cache slot}; k_cache / v_cache rows of a slot are max_seq apart; talk NULL:
+// no mixing.
+extern "C" size_t b200_attn_prefill_mixed_plane_floats(int n_seqs, int max_q_len, int64_t s_ld) {
+  return (size_t)n_seqs * (size_t)((max_q_len + kPfBM - 1) / kPfBM) * (size_t)(s_ld / kPfBN) * (kPfBM * kPfBN);
+}
+
 extern "C" int b200_attn_prefill_mixed(const void* q, int64_t ldq, const void* k_cache, int64_t ldk, const void* v_cache, int64_t ldv,
-                                       const int32_t* seqs, int n_seqs, int max_q_len, int max_seq, const int32_t* row_pos, int64_t rows,
-                                       const void* talk, const void* sink, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size,
-                                       float scale, float* sbuf, int64_t s_ld, b200_stream_t stream) {
-  B200_CHECK_ARG(q && k_cache && v_cache && seqs && row_pos && y && sbuf, "b200_attn_prefill_mixed: null pointer");
-  B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && rows > 0 && rows <= 0x7fffffff && n_head > 0 && n_head <= 64 && n_kv_head > 0 &&
-                     n_head % n_kv_head == 0 && max_seq > 0, "b200_attn_prefill_mixed: bad shape (at most 64 heads)");
+                                       const int32_t* seqs, int n_seqs, int max_q_len, int max_seq, const void* talk, const void* sink, void* y,
+                                       int64_t ldy, int n_head, int n_kv_head, int head_size, float scale, float* sbuf, int64_t s_ld,
+                                       b200_stream_t stream) {
+  B200_CHECK_ARG(q && k_cache && v_cache && seqs && y && sbuf, "b200_attn_prefill_mixed: null pointer");
+  B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && n_head > 0 && n_head <= 64 && n_kv_head > 0 && n_head % n_kv_head == 0 && max_seq > 0 &&
+                     s_ld > 0, "b200_attn_prefill_mixed: bad shape (at most 64 heads)");
   B200_CHECK_ARG(head_size == 64 || head_size == 128, "b200_attn_prefill_mixed: head_size must be 64 or 128 (got %d)", head_size);
-  B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0 && (s_ld & 63) == 0, "b200_attn_prefill_mixed: leading dimensions must be multiples of 8 elements, the planes' of 64");
+  B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0 && (s_ld & 63) == 0, "b200_attn_prefill_mixed: leading dimensions must be multiples of 8 elements, the context bound of 64");
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
                    reinterpret_cast<uintptr_t>(seqs) | reinterpret_cast<uintptr_t>(sbuf)) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 3) == 0,
                  "b200_attn_prefill_mixed: operands must be 16-byte aligned");
+  const int s_qt = (max_q_len + kPfBM - 1) / kPfBM, s_kt = (int)(s_ld / kPfBN);
+  const int64_t s_h = (int64_t)b200_attn_prefill_mixed_plane_floats(n_seqs, max_q_len, s_ld);
+  B200_CHECK_ARG((int64_t)n_seqs * s_qt * s_kt <= 0x7fffffff, "b200_attn_prefill_mixed: too many tiles");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0,
-                  reinterpret_cast<const __nv_bfloat16*>(sink), 0, nullptr, 0, nullptr, 0, 0, sbuf, rows * s_ld, s_ld, max_seq};
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 0, nullptr, 0, nullptr, 0, 0, sbuf, s_h, s_qt, s_kt, max_seq};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 0, 1>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t, 0, 1>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   if (talk) {
-    const dim3 grid((unsigned)rows, (unsigned)((s_ld + 255) / 256));
+    const dim3 grid((unsigned)(n_seqs * s_qt * s_kt), 8);
     const __nv_bfloat16* tk = reinterpret_cast<const __nv_bfloat16*>(talk);
-    if (n_head <= 8) B200_CUDA(launch(mix_scores_kernel<8>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
-    else if (n_head <= 16) B200_CUDA(launch(mix_scores_kernel<16>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
-    else if (n_head <= 32) B200_CUDA(launch(mix_scores_kernel<32>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
-    else B200_CUDA(launch(mix_scores_kernel<64>, grid, dim3(256), 0, st, sbuf, rows * s_ld, s_ld, tk, row_pos, n_head));
+    const int4* sq = reinterpret_cast<const int4*>(seqs);
+    if (n_head <= 8) B200_CUDA(launch(mix_scores_kernel<8>, grid, dim3(256), 0, st, sbuf, s_h, s_qt, s_kt, tk, sq, n_head));
+    else if (n_head <= 16) B200_CUDA(launch(mix_scores_kernel<16>, grid, dim3(256), 0, st, sbuf, s_h, s_qt, s_kt, tk, sq, n_head));
+    else if (n_head <= 32) B200_CUDA(launch(mix_scores_kernel<32>, grid, dim3(256), 0, st, sbuf, s_h, s_qt, s_kt, tk, sq, n_head));
+    else B200_CUDA(launch(mix_scores_kernel<64>, grid, dim3(256), 0, st, sbuf, s_h, s_qt, s_kt, tk, sq, n_head));
   }
   // the planes are in the log2 domain already: the last pass scales by 1
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 0, 2>(q, k_cache, v_cache, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, 0.6931471805599453f, st, &vw)));
@@ -437,7 +453,7 @@ extern "C" int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_ragged: operands must be 16-byte aligned");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0, nullptr, 0,
-                  nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0};
+                  nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
@@ -457,7 +473,7 @@ extern "C" int b200_attn_prefill_window(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_window: operands must be 16-byte aligned");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), window,
-                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0};
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
@@ -482,7 +498,7 @@ extern "C" int b200_attn_prefill_shared(const void* q, int64_t ldq, const void* 
                  "b200_attn_prefill_shared: operands must be 16-byte aligned");
   const PfView vw{0, head_size + dk2, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0,
                   reinterpret_cast<const __nv_bfloat16*>(sink), 0, reinterpret_cast<const __nv_bfloat16*>(k2), ldk2,
-                  reinterpret_cast<const __nv_bfloat16*>(gate), ldg, gate_mode, nullptr, 0, 0, 0};
+                  reinterpret_cast<const __nv_bfloat16*>(gate), ldg, gate_mode, nullptr, 0, 0, 0, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128 && dk2 == 64) B200_CUDA((launch_prefill<128, int32_t, 64>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   else if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t, 128>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));

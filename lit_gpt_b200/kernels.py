@@ -1042,37 +1042,29 @@ TALK_PREFILL_PLANE_BYTES = 8 << 30
 
 def talk_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seqs: torch.Tensor, max_q_len: int, n_head: int, n_kv_head: int, dk: int,
               dv: int, max_seq: int, scale: float, n_split: int = 1, *, talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
-              row_pos: Optional[torch.Tensor] = None, context: int = 0) -> torch.Tensor:
+              context: int = 0) -> torch.Tensor:
     """Causal attention over cached keys and values whose scores are mixed over the heads by `talk` (H, H) before the softmax, with an
     optional sink logit per head.  q (n, H * dk); k_cache / v_cache: 2-d views (slots * max_seq, G * dk | G * dv) of the cache rows;
-    seqs int32 (S, 4) = first row, rows, first position, cache slot.  Returns (n, H * dv).  With `row_pos` (int32 (n,), each row's
-    position) and `context` (an upper bound of position + 1), bf16 prompts with dk = dv in {64, 128} run on the tensor-core tiles
-    over fp32 score planes (n_head, n, context)."""
-    C.require_cuda(q, k_cache, v_cache, seqs, talk, sink, row_pos)
+    seqs int32 (S, 4) = first row, rows, first position, cache slot.  Returns (n, H * dv).  With `context` (an upper bound of any row's
+    position + 1), bf16 prompts with dk = dv in {64, 128} run on the tensor-core tiles over fp32 score planes."""
+    C.require_cuda(q, k_cache, v_cache, seqs, talk, sink)
     n = q.shape[0]
     s_ld = -(-max(context, 1) // 64) * 64
-    if (row_pos is not None and context > 0 and TALK_PREFILL_MMA and q.dtype == torch.bfloat16 and k_cache.dtype == v_cache.dtype == torch.bfloat16
+    lib = C.load_core()
+    if (context > 0 and TALK_PREFILL_MMA and q.dtype == torch.bfloat16 and k_cache.dtype == v_cache.dtype == torch.bfloat16
             and dk == dv and dk in (64, 128) and n_head <= 64 and max_q_len >= TALK_PREFILL_MMA_MIN_ROWS
-            and n_head * n * s_ld * 4 <= TALK_PREFILL_PLANE_BYTES and row_pos.dtype == torch.int32 and row_pos.is_contiguous()
             and seqs.dtype == torch.int32 and seqs.is_contiguous() and q.stride(-1) == k_cache.stride(-1) == v_cache.stride(-1) == 1
             and not (q.stride(0) | k_cache.stride(0) | v_cache.stride(0)) & 7
             and not (q.data_ptr() | k_cache.data_ptr() | v_cache.data_ptr() | seqs.data_ptr()) & 15
             and all(t is None or (t.dtype == torch.bfloat16 and t.is_contiguous()) for t in (talk, sink))):
-        planes = torch.empty((n_head, n, s_ld), dtype=torch.float32, device=q.device)
-        out = torch.empty((n, n_head * dv), dtype=q.dtype, device=q.device)
-        C.check(C.load_core().b200_attn_prefill_mixed(q.data_ptr(), q.stride(0), k_cache.data_ptr(), k_cache.stride(0), v_cache.data_ptr(), v_cache.stride(0),
-                                                      seqs.data_ptr(), seqs.shape[0], max_q_len, max_seq, row_pos.data_ptr(), n, C.ptr(talk), C.ptr(sink),
-                                                      out.data_ptr(), out.stride(0), n_head, n_kv_head, dk, float(scale), planes.data_ptr(), s_ld,
-                                                      C.stream_ptr(q.device)), "attn_prefill_mixed")
-        return out
-    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
-        raise C.B200Error("talk_attn: seqs must be contiguous int32 (S, 4)")
-    if not (q.dtype == k_cache.dtype == v_cache.dtype) or q.stride(-1) != 1 or k_cache.stride(-1) != 1 or v_cache.stride(-1) != 1:
-        raise C.B200Error("talk_attn: q and the caches of one dtype with unit inner stride")
-    for t in (talk, sink):
-        if t is not None and (t.dtype != q.dtype or not t.is_contiguous()):
-            raise C.B200Error("talk_attn: talk and sink must be contiguous and of the queries' dtype")
-    lib = C.load_core()
+        plane = lib.b200_attn_prefill_mixed_plane_floats(seqs.shape[0], max_q_len, s_ld)
+        if n_head * plane * 4 <= TALK_PREFILL_PLANE_BYTES:
+            planes = torch.empty((n_head, plane), dtype=torch.float32, device=q.device)
+            out = torch.empty((n, n_head * dv), dtype=q.dtype, device=q.device)
+            C.check(lib.b200_attn_prefill_mixed(q.data_ptr(), q.stride(0), k_cache.data_ptr(), k_cache.stride(0), v_cache.data_ptr(), v_cache.stride(0),
+                                                seqs.data_ptr(), seqs.shape[0], max_q_len, max_seq, C.ptr(talk), C.ptr(sink), out.data_ptr(), out.stride(0),
+                                                n_head, n_kv_head, dk, float(scale), planes.data_ptr(), s_ld, C.stream_ptr(q.device)), "attn_prefill_mixed")
+            return out
     ws = _ws("talk", q.device, lib.b200_talk_attn_workspace_bytes(n, n_head, dv, n_split))
     out = torch.empty((n, n_head * dv), dtype=q.dtype, device=q.device)
     args = C.TalkAttnArgs(q=q.data_ptr(), ldq=q.stride(0), k_cache=k_cache.data_ptr(), ldk=k_cache.stride(0), v_cache=v_cache.data_ptr(),

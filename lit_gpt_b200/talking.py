@@ -89,5 +89,5 @@ class TalkingHeadsAttention(nn.Module):
                     K.rope_seg(v, cache.value_rows, G, dv, out_rows=batch.cache_rows), dtype=h.dtype, device=h.device)
         splits = decode_splits(batch.context_hint, batch.seq_state.shape[0]) if batch.decode else 1
         y = K.talk_attn(q, cache.key_rows, cache.value_rows, batch.seq_state, batch.max_q_len, H, G, dk, dv, cache.keys.shape[1], s.scale, splits,
-                        talk=self.talk, sink=self.sink, row_pos=None if batch.decode else batch.row_pos, context=batch.context_hint)
+                        talk=self.talk, sink=self.sink, context=0 if batch.decode else batch.context_hint)
         return F.linear(y, self.w_o)

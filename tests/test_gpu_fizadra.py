@@ -388,19 +388,16 @@ def test_mixed_score_attention_kernel(dtype, sizes):
     assert rel_err(got, want) < tol, rel_err(got, want)
     if dtype == torch.bfloat16 and dk == dv and dk in (64, 128):
         # the same prompts on the tensor-core tiles: raw scores into fp32 planes, mixing in place, softmax and values from the planes
-        rp = torch.tensor(list(range(101)) + list(range(37, 87)), dtype=torch.int32, device="cuda")
         for tk in (talk.cuda(), None):
             launches = k.launch_count()
-            got = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, talk=tk, sink=sink.cuda(), row_pos=rp,
-                              context=101)
+            got = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, talk=tk, sink=sink.cuda(), context=101)
             assert k.launch_count() - launches == (3 if tk is not None else 2)
             if tk is not None:
                 assert rel_err(got, want) < 3e-2, rel_err(got, want)
             else:
                 k.TALK_PREFILL_MMA = False
                 try:
-                    other = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, sink=sink.cuda(), row_pos=rp,
-                                        context=101)
+                    other = k.talk_attn(q.cuda(), kg.view(-1, G * dk), vg.view(-1, G * dv), seqs, 101, H, G, dk, dv, L, scale, 1, sink=sink.cuda(), context=101)
                 finally:
                     k.TALK_PREFILL_MMA = True
                 assert rel_err(got, other) < 3e-2
