@@ -273,7 +273,7 @@ def _latent_reference(q, c, kr, w_uk, w_uv, sink, gate, H, dn, dr, dv, scale, st
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(3, 10, 6, 7, 12), (4, 24, 32, 136, 64), (16, 16, 32, 8, 64), (2, 64, 64, 128, 96), (2, 64, 64, 64, 96),
-                                   (3, 128, 64, 128, 64), (2, 64, 128, 64, 32)])
+                                   (3, 128, 64, 128, 64), (2, 64, 128, 64, 32), (2, 128, 128, 128, 32)])
 @pytest.mark.parametrize("options", ["sink+element", "head", "none"])
 def test_latent_attention_kernels_with_a_shared_key_part(dtype, sizes, options):
     """Prompt tiles (a sequence from position 0 and one continuing at position 70, together) and single rows (any-size and, for
@@ -684,3 +684,20 @@ def test_prompts_on_the_tensor_cores_then_decoding(dtype):
     assert_close(torch.cat(got["a"]), want["a"][160:190], dtype, "a")
     assert_close(torch.cat(got["b"]), want["b"][65:95], dtype, "b")
     assert_close(torch.cat(got["c"]), want["c"], dtype, "c")
+
+
+def test_generate_command_line(tmp_path):
+    """`python -m lit_gpt_b200.generate.base` on a checkpoint directory without a tokenizer: a prompt of token ids in, the oracle's greedy
+    continuation out."""
+    import subprocess
+
+    cfg = CFG_ODD
+    w = checkpoint(cfg, 111)
+    _write_checkpoint(tmp_path, cfg, w)
+    prompt = tokens_for(cfg, 6, 112)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-m", "lit_gpt_b200.generate.base", " ".join(str(t) for t in prompt), "--checkpoint_dir", str(tmp_path),
+                          "--precision", "32-true", "--temperature", "0", "--max_new_tokens", "9"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    printed = [int(t) for t in res.stdout.strip().splitlines()[-1].split()]
+    assert printed == O.greedy(cfg, w, prompt, 9)
