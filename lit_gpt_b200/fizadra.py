@@ -21,7 +21,7 @@ CUDA-graph capturable) and ``step`` over ragged batches for ``generate.serve.Ses
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn
