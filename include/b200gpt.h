@@ -442,8 +442,10 @@ int b200_latent_decode_tune(int force_any_size_kernel);
 
 /* Router: s = sigmoid(W_router x), or softmax over all experts with B200_ROUTE_SOFTMAX; experts are chosen by s + correction among
  * the `keep` best of `n_group` equal groups of neighbours (group rank = sum of its two largest corrected scores, or the largest
- * with B200_ROUTE_GROUP_MAX); weights[t, k] = s of the chosen expert, not renormalised. */
-enum b200_route_flags { B200_ROUTE_SOFTMAX = 1, B200_ROUTE_GROUP_MAX = 2 };
+ * with B200_ROUTE_GROUP_MAX); weights[t, k] = s of the chosen expert, not renormalised.  B200_ROUTE_TOPK_SOFTMAX: s is the raw logit,
+ * the largest logits are chosen and the weights are a softmax over the chosen logits only.  B200_ROUTE_BIAS: `correction` is a bias
+ * added to the logit itself (it enters the scores) instead of a selection-only term. */
+enum b200_route_flags { B200_ROUTE_SOFTMAX = 1, B200_ROUTE_GROUP_MAX = 2, B200_ROUTE_TOPK_SOFTMAX = 4, B200_ROUTE_BIAS = 8 };
 int b200_moe_route(const void* x, const void* w_router, const void* correction, int32_t* ids, float* weights, int64_t tokens, int d,
                    int n_expert, int top, int n_group, int keep, int flags, int dtype, b200_stream_t stream);
 /* counting sort of the (token, choice) pairs by expert: expert_off[E + 1], tile_off[E + 1] (64-row tiles), slot_token[tokens * top],
@@ -453,10 +455,11 @@ int b200_moe_plan(const int32_t* ids, int64_t tokens, int top, int n_expert, int
 /* c[row, :n] = act(a[row_src ? row_src[row] : row, :k] . w[e][:n, :k]^T) for the rows of every expert e; act = relu^2 or none */
 int b200_moe_gemm(const void* a, int64_t lda, const int32_t* row_src, const void* w, void* c, int64_t ldc, const int32_t* expert_off,
                   const int32_t* tile_off, int64_t rows, int n_expert, int n, int k, int sqrelu, int dtype, b200_stream_t stream);
-/* few tokens: hidden = relu(W_up[e] x)^2 per (token, choice) -- gated: silu(W_up[e][:ff] x) * (W_up[e][ff:] x) with 2 ff rows per
- * expert --, out[t] = sum_k weights[t, k] * W_down[e_k] hidden[t, k] */
+/* few tokens: hidden = relu(W_up[e] x)^2 per (token, choice) -- gated 1: silu(W_up[e][:ff] x) * (W_up[e][ff:] x) with 2 ff rows per
+ * expert; gated 2: g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit) --,
+ * out[t] = sum_k weights[t, k] * W_down[e_k] hidden[t, k] */
 int b200_moe_gemv(const void* x, const int32_t* ids, const float* weights, const void* w_up, const void* w_down, void* hidden, void* out,
-                  int64_t tokens, int top, int d, int ff, int gated, int dtype, b200_stream_t stream);
+                  int64_t tokens, int top, int d, int ff, int gated, float limit, float alpha, int dtype, b200_stream_t stream);
 int b200_moe_combine(const void* y, const int32_t* slot_of, const float* weights, void* out, int64_t tokens, int top, int d, int dtype,
                      b200_stream_t stream);
 
@@ -466,6 +469,12 @@ int b200_moe_combine(const void* y, const int32_t* slot_of, const float* weights
 int b200_attn_prefill_window(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
                              int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale,
                              int window, const void* sink, b200_stream_t stream);
+/* The same with a distance bias (score -= r1[h] ln(1 + r2[h] (i - j)); both NULL: none) and a sigmoid output gate (gate_mode 0 none,
+ * 1 gate[row, h], 2 gate[row, h * head_size + c]; rows ldg apart), all bf16. */
+int b200_attn_prefill_window_ex(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
+                                int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale,
+                                int window, const void* sink, const void* r1, const void* r2, const void* gate, int64_t ldg, int gate_mode,
+                                b200_stream_t stream);
 
 /* ---- sequence-state mechanisms: short convolutions, the gated delta rule, windowed attention over a ring -------------------
  * A step's rows are the new tokens of several sequences packed one after another; seqs[s] = {first row, rows, position of the
@@ -484,6 +493,21 @@ int b200_sandwich_residual(const b200_sandwich_args* args, b200_stream_t stream)
 int b200_activation(void* x, int64_t n, int kind, int dtype, b200_stream_t stream);
 /* out[r, c] = act(in[r, c]) * in[r, ff + c] for in (rows, 2 ff) */
 int b200_glu(const void* in, void* out, int64_t rows, int ff, int kind, int dtype, b200_stream_t stream);
+/* in place: xIELU with its two raw parameters params[0..1] (in `dtype`): z > 0: softplus(p) z^2 + z / 2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 */
+int b200_xielu(void* x, int64_t n, const void* params, int dtype, b200_stream_t stream);
+/* in (rows, 2 ff) = [gate | up] -> out (rows, ff) = g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit) */
+int b200_glu_clamped(const void* in, void* out, int64_t rows, int ff, float limit, float alpha, int dtype, b200_stream_t stream);
+/* x += y0 * s0 + (y1 + y2) * s1 + extra + row_add (fp32 stream, in place; every term optional, a NULL scale is 1; s0, s1, row_add are
+ * d numbers, extra fp32 rows); cast = dtype(x) (optional); act = dtype(tanh(alpha[0] * x) * nw + nb) (nw NULL: skipped) */
+typedef struct b200_scaled_residual_args {
+  const void* y0; const void* s0; const void* y1; const void* y2; const void* s1;
+  const float* extra; const void* row_add;
+  float* x; void* cast;
+  const void* alpha; const void* nw; const void* nb; void* act;
+  int64_t rows;
+  int d, dtype;
+} b200_scaled_residual_args;
+int b200_scaled_residual(const b200_scaled_residual_args* args, b200_stream_t stream);
 
 /* One group of heads of a short causal convolution (see b200_short_conv). */
 typedef struct b200_conv_group {
@@ -546,6 +570,10 @@ typedef struct b200_window_attn_args {
   int dtype;
   const int32_t* row_seq;   /* given (with rows): the step's rows also enter the rings, as b200_ring_store does; NULL: rings untouched */
   int64_t rows;
+  /* optional: score -= dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (both n_head numbers in `dtype`, or both NULL) */
+  const void* dist_r1; const void* dist_r2;
+  /* optional: the output is multiplied by sigmoid(gate[row, h]) (gate_mode 1) or sigmoid(gate[row, h * dv + c]) (gate_mode 2); rows ldg apart */
+  const void* gate; int64_t ldg; int gate_mode;
 } b200_window_attn_args;
 int b200_window_attn(const b200_window_attn_args* args, b200_stream_t stream);
 /* test knob: non-zero keeps single-row steps on the tiled kernel; returns the previous setting */

@@ -137,10 +137,17 @@ class WindowAttnArgs(ctypes.Structure):  # mirrors b200_window_attn_args
     _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p), ("ldq", c_int64), ("ldk", c_int64), ("ldv", c_int64),
                 ("ldo", c_int64), ("k_ring", c_void_p), ("v_ring", c_void_p), ("sink", c_void_p), ("seqs", c_void_p), ("n_seqs", c_int),
                 ("max_q_len", c_int), ("ring", c_int), ("n_head", c_int), ("n_kv_head", c_int), ("dk", c_int), ("dv", c_int), ("window", c_int),
-                ("scale", c_float), ("dtype", c_int), ("row_seq", c_void_p), ("rows", c_int64)]
+                ("scale", c_float), ("dtype", c_int), ("row_seq", c_void_p), ("rows", c_int64), ("dist_r1", c_void_p), ("dist_r2", c_void_p),
+                ("gate", c_void_p), ("ldg", c_int64), ("gate_mode", c_int)]
 
 
-ROUTE_SOFTMAX, ROUTE_GROUP_MAX = 1, 2
+class ScaledResidualArgs(ctypes.Structure):  # mirrors b200_scaled_residual_args
+    _fields_ = [("y0", c_void_p), ("s0", c_void_p), ("y1", c_void_p), ("y2", c_void_p), ("s1", c_void_p), ("extra", c_void_p), ("row_add", c_void_p),
+                ("x", c_void_p), ("cast", c_void_p), ("alpha", c_void_p), ("nw", c_void_p), ("nb", c_void_p), ("act", c_void_p), ("rows", c_int64),
+                ("d", c_int), ("dtype", c_int)]
+
+
+ROUTE_SOFTMAX, ROUTE_GROUP_MAX, ROUTE_TOPK_SOFTMAX, ROUTE_BIAS = 1, 2, 4, 8
 ACT_GELU, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = 0, 1, 2, 3
 
 # Entry points of the sources every model needs (library state, norms, sampling) and of the fp32-residual / latent-attention /
@@ -166,11 +173,15 @@ _CORE_SIGNATURES = {
     "b200_moe_plan": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_moe_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                               c_void_p]),
-    "b200_moe_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float, c_float,
+                              c_int, c_void_p]),
     "b200_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "b200_sandwich_residual": (c_int, [ctypes.POINTER(SandwichArgs), c_void_p]),
     "b200_activation": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p]),
     "b200_glu": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_xielu": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p]),
+    "b200_glu_clamped": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_int, c_void_p]),
+    "b200_scaled_residual": (c_int, [ctypes.POINTER(ScaledResidualArgs), c_void_p]),
     "b200_short_conv": (c_int, [c_void_p, c_int64, ctypes.POINTER(ConvGroup), c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int,
                                 c_void_p]),
     "b200_conv_tail_update": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_void_p]),
@@ -189,6 +200,8 @@ _CORE_SIGNATURES = {
     "b200_talk_attn": (c_int, [ctypes.POINTER(TalkAttnArgs), c_void_p]),
     "b200_attn_prefill_window": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,
                                          c_int, c_float, c_int, c_void_p, c_void_p]),
+    "b200_attn_prefill_window_ex": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,
+                                            c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200_ring_store": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,
                                 c_void_p]),
 }

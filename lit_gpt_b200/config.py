@@ -599,10 +599,141 @@ class FizadraConfig:
             return cls.from_dict(json.load(fp))
 
 
+@dataclass
+class GatedWindowSpec:
+    """Sliding-window attention with a sigmoid output gate: optional biases on the q, k, v projections, optional rotary positions
+    (half-split pairs) on q and k, an optional distance bias (score -= r1_h ln(1 + r2_h (i - j)), two learned numbers per head), and
+    a gate per output number ("element") or per head ("head") projected from the mixer's input."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    window: int                    # a position sees itself and the window - 1 before it
+    scale: float
+    rot: Optional[RotarySpec] = None
+    bias: bool = False
+    distance: bool = False
+    gate: Optional[str] = "element"
+
+
+@dataclass
+class ClampedMoESpec:
+    """Experts chosen by the largest biased router logits, weighted by a softmax over the chosen logits only; expert:
+    W_down (g sigmoid(alpha g) (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit); optionally a shared expert of
+    the same form (its own ff and limit) that every token uses."""
+
+    experts: int
+    top: int
+    ff: int
+    limit: float
+    alpha: float = 1.702
+    shared_ff: int = 0             # 0: no shared expert
+    shared_limit: float = 0.0
+
+
+@dataclass
+class NulezenLayerSpec:
+    type: str                      # "attention" (distance bias, gate per number) | "attention_2" (biases, rotary, gate per head)
+    mixer: GatedWindowSpec
+    mlp: Any = None                # DenseMLPSpec | ClampedMoESpec | None
+
+
+@dataclass
+class NulezenConfig:
+    """Nulezen: parallel blocks over an fp32 residual stream -- one dynamic-tanh norm feeds the mixer and the feed-forward, whose results
+    join the stream scaled per channel.  Mixers: two kinds of gated sliding-window attention; feed-forwards: dense with xIELU, or
+    clamped gated experts with a shared expert.  With `loop_times` > 0 the layers loop_start .. loop_stop - 1 run loop_times times with
+    the same weights (each pass with its own cache); every pass starts from a projection of [stream | embedding] plus a vector of the
+    pass.  The head is the embedding table."""
+
+    name: str = "Nulezen"
+    vocab_size: int = 0
+    n_embd: int = 0
+    norm_eps: float = 1e-5
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    layers: List[NulezenLayerSpec] = field(default_factory=list)
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 0            # 0: no loop (no entry projection either)
+    block_size: int = 1 << 30      # constant-size state, no position table: positions are bounded by int32 only
+
+    def __post_init__(self) -> None:
+        self.padded_vocab_size = self.vocab_size
+        self.n_layer = len(self.layers)
+        if self.loop_times < 0 or not 0 <= self.loop_start <= self.loop_stop <= self.n_layer:
+            raise ValueError(f"loop {self.loop_start}..{self.loop_stop} x {self.loop_times} does not fit {self.n_layer} layers")
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            if layer.type not in ("attention", "attention_2"):
+                raise ValueError(f"layer {i}: unknown mixer type {layer.type!r}")
+            if m.heads < 1 or m.kv_heads < 1 or m.heads % m.kv_heads or m.window < 1 or m.dim < 1 or m.vdim < 1:
+                raise ValueError(f"layer {i}: bad attention shape")
+            if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim):
+                raise ValueError(f"layer {i}: rotary dimensions must be even and at most the head size")
+            if m.gate not in (None, "element", "head"):
+                raise ValueError(f"layer {i}: unknown gate kind {m.gate!r}")
+            e = layer.mlp
+            if isinstance(e, ClampedMoESpec) and (not 0 < e.top <= e.experts or e.limit <= 0 or (e.shared_ff and e.shared_limit <= 0)):
+                raise ValueError(f"layer {i}: bad expert shape (top {e.top} of {e.experts}, limits must be positive)")
+
+    @property
+    def looped(self) -> bool:
+        return self.loop_times > 0 and self.loop_stop > self.loop_start
+
+    def schedule(self) -> List[Tuple[int, int, int]]:
+        """The layer runs in order: (layer index, state index, number of the pass this run opens or -1).  Every run has a state of
+        its own."""
+        if not self.looped:
+            return [(i, i, -1) for i in range(self.n_layer)]
+        order = [(i, -1) for i in range(self.loop_start)]
+        for t in range(self.loop_times):
+            order += [(i, t if i == self.loop_start else -1) for i in range(self.loop_start, self.loop_stop)]
+        order += [(i, -1) for i in range(self.loop_stop, self.n_layer)]
+        return [(i, n, t) for n, (i, t) in enumerate(order)]
+
+    @classmethod
+    def from_dict(cls, js: Dict[str, Any]) -> "NulezenConfig":
+        layers = []
+        for i, entry in enumerate(js["layers"]):
+            mx, kind = entry["mixer"], entry["type"]
+            if kind not in ("attention", "attention_2"):
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            second = kind == "attention_2"
+            rot = mx.get("rot") if second else None
+            mixer = GatedWindowSpec(heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
+                                    vdim=int(mx.get("vdim", mx["dim"])), window=int(mx["mask"]["size"]), scale=float(mx["scale"]),
+                                    rot=RotarySpec.from_dict(rot, interleaved=False) if rot and int(rot["dims"]) > 0 else None,
+                                    bias=second, distance=not second, gate="head" if second else "element")
+            mlp: Any = None
+            ml = entry.get("mlp")
+            if ml is not None:
+                if ml.get("kind") == "dense":
+                    mlp = DenseMLPSpec(ff=int(ml["ff"]))
+                elif ml.get("kind") == "moe":
+                    sh = ml.get("shared") or {}
+                    mlp = ClampedMoESpec(experts=int(ml["router"]["experts"]), top=int(ml["router"]["top"]), ff=int(ml["expert"]["ff"]),
+                                         limit=float(ml["expert"]["limit"]), shared_ff=int(sh.get("ff", 0)), shared_limit=float(sh.get("limit", 0.0)))
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {ml.get('kind')!r}")
+            layers.append(NulezenLayerSpec(type=kind, mixer=mixer, mlp=mlp))
+        loop = js.get("loop") or {}
+        return cls(name=js.get("architecture", "Nulezen"), vocab_size=int(js["vocab"]), n_embd=int(js["width"]), norm_eps=float(js["norm"]["eps"]),
+                   embedding_scale=float((js.get("embedding") or {}).get("scale", 1.0)), logit_scale=float(js.get("logit_scale", 1.0)), layers=layers,
+                   loop_start=int(loop.get("start", 0)), loop_stop=int(loop.get("stop", loop.get("start", 0))), loop_times=int(loop.get("times", 0)))
+
+    @classmethod
+    def from_json(cls, path: Union[str, Path]) -> "NulezenConfig":
+        with open(path, encoding="utf-8") as fp:
+            return cls.from_dict(json.load(fp))
+
+
 # "architecture" value of config.json -> (configuration class, "module:class" of the model)
 architectures: Dict[str, Any] = {"Pomipel": (PomipelConfig, "lit_gpt_b200.pomipel:Pomipel"),
                                  "Lefalix": (LefalixConfig, "lit_gpt_b200.lefalix:Lefalix"),
-                                 "Fizadra": (FizadraConfig, "lit_gpt_b200.fizadra:Fizadra")}
+                                 "Fizadra": (FizadraConfig, "lit_gpt_b200.fizadra:Fizadra"),
+                                 "Nulezen": (NulezenConfig, "lit_gpt_b200.nulezen:Nulezen")}
 
 
 def load_config(checkpoint_dir: Union[str, Path], **kwargs: Any) -> Any:

@@ -54,6 +54,9 @@ struct PfView {
   int64_t s_h;
   int s_qt, s_kt;
   int64_t kv_slot_rows;
+  // ragged only: a distance bias, score -= dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (both NULL: none)
+  const __nv_bfloat16* dist_r1;
+  const __nv_bfloat16* dist_r2;
 };
 
 template <int HS, typename PosT, int HK2 = 0, int MODE = 0>
@@ -179,6 +182,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   const int warp_lim = wl;
+  // distance bias on the raw dot products: (s - r1 log2(1 + r2 dist) / scale_log2) * scale_log2 is the biased score in the log2 domain
+  const bool biased = MODE == 0 && vw.seqs && vw.dist_r1;
+  const float r1q = biased ? __bfloat162float(vw.dist_r1[h]) / scale_log2 : 0.f, r2h = biased ? __bfloat162float(vw.dist_r2[h]) : 0.f;
   for (int tile = tile_lo; tile < ntiles; ++tile) {
     const int buf = tile & 1;
     if (tile + 1 < ntiles) { load_kv(tile + 1, buf ^ 1); pf_wait<1>(); } else { pf_wait<0>(); }
@@ -231,6 +237,17 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const bool need_mask = j0 + kPfBN - 1 > min(limA < 0 ? 0x7fffffff : limA, limB < 0 ? 0x7fffffff : limB) || limA < 0 || limB < 0 ||
                              (window > 0 && j0 < max(loA, loB));
       float tmA = -INFINITY, tmB = -INFINITY;
+      if (biased) {   // entries ahead of the row get a meaningless bias and are masked below
+#pragma unroll
+        for (int i = 0; i < kPfBN / 8; ++i) {
+          const int j = j0 + i * 8 + 2 * tq;
+          const float dA = (float)max(limA - j, 0), dB = (float)max(limB - j, 0);
+          s[i][0] -= r1q * log2f(fmaf(r2h, dA, 1.0f));
+          s[i][1] -= r1q * log2f(fmaf(r2h, fmaxf(dA - 1.0f, 0.f), 1.0f));
+          s[i][2] -= r1q * log2f(fmaf(r2h, dB, 1.0f));
+          s[i][3] -= r1q * log2f(fmaf(r2h, fmaxf(dB - 1.0f, 0.f), 1.0f));
+        }
+      }
 #pragma unroll
       for (int i = 0; i < kPfBN / 8; ++i) {
         if (need_mask) {
@@ -465,7 +482,16 @@ extern "C" int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* 
 extern "C" int b200_attn_prefill_window(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
                                         int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale,
                                         int window, const void* sink, b200_stream_t stream) {
+  return b200_attn_prefill_window_ex(q, ldq, k, ldk, v, ldv, seqs, n_seqs, max_q_len, y, ldy, n_head, n_kv_head, head_size, scale, window, sink,
+                                     nullptr, nullptr, nullptr, 0, 0, stream);
+}
+
+extern "C" int b200_attn_prefill_window_ex(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
+                                           int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale,
+                                           int window, const void* sink, const void* r1, const void* r2, const void* gate, int64_t ldg,
+                                           int gate_mode, b200_stream_t stream) {
   B200_CHECK_ARG(q && k && v && seqs && y, "b200_attn_prefill_window: null pointer");
+  B200_CHECK_ARG(!r1 == !r2 && gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0 || gate), "b200_attn_prefill_window: bad distance bias or gate");
   B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && n_head > 0 && n_head <= 65535 && n_kv_head > 0 && n_head % n_kv_head == 0 &&
                  window >= 0, "b200_attn_prefill_window: bad shape");
   B200_CHECK_ARG(head_size == 64 || head_size == 128, "b200_attn_prefill_window: head_size must be 64 or 128 (got %d)", head_size);
@@ -473,7 +499,8 @@ extern "C" int b200_attn_prefill_window(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_window: operands must be 16-byte aligned");
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), window,
-                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0, 0};
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, gate_mode ? reinterpret_cast<const __nv_bfloat16*>(gate) : nullptr, ldg,
+                  gate_mode, nullptr, 0, 0, 0, 0, reinterpret_cast<const __nv_bfloat16*>(r1), reinterpret_cast<const __nv_bfloat16*>(r2)};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));

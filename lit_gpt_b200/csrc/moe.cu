@@ -51,9 +51,11 @@ __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restri
   for (int e = warp; e < n_expert; e += kRtThreads / 32) {
     const float z = warp_dot(xr, w_router + (int64_t)e * d, d, lane);
     if (lane == 0) {
-      const float s = (flags & B200_ROUTE_SOFTMAX) ? z : 1.0f / (1.0f + expf(-z));
+      const float corr = correction ? load_as_float(correction, e) : 0.f;
+      const float zz = (flags & B200_ROUTE_BIAS) ? z + corr : z;     // a bias is part of the logit; a correction only steers the choice
+      const float s = (flags & (B200_ROUTE_SOFTMAX | B200_ROUTE_TOPK_SOFTMAX)) ? zz : 1.0f / (1.0f + expf(-zz));
       score[e] = s;
-      choice[e] = s + (correction ? load_as_float(correction, e) : 0.f);
+      choice[e] = (flags & B200_ROUTE_BIAS) ? s : s + corr;
     }
   }
   __syncthreads();
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restri
       for (int e = lane; e < n_expert; e += 32) {
         const float s = expf(score[e] - mx) / sum;
         score[e] = s;
-        choice[e] = s + (correction ? load_as_float(correction, e) : 0.f);
+        choice[e] = s + (correction && !(flags & B200_ROUTE_BIAS) ? load_as_float(correction, e) : 0.f);
       }
     }
     __syncthreads();
@@ -105,6 +107,12 @@ __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restri
       choice[e] = -INFINITY;
     }
     __syncwarp();
+  }
+  if ((flags & B200_ROUTE_TOPK_SOFTMAX) && lane == 0) {   // weights = softmax over the chosen logits only
+    float mx = -INFINITY, sum = 0.f;
+    for (int k = 0; k < top; ++k) mx = fmaxf(mx, score[ids[t * top + k]]);
+    for (int k = 0; k < top; ++k) sum += expf(score[ids[t * top + k]] - mx);
+    for (int k = 0; k < top; ++k) wts[t * top + k] = expf(score[ids[t * top + k]] - mx) / sum;
   }
 }
 
@@ -223,9 +231,10 @@ __global__ void __launch_bounds__(kGmThreads) moe_gemm_kernel(const T* __restric
 
 // decode: hidden[p, f] = relu(W_up[ids[p]][f, :] . x[p / top, :])^2 for the pair p = t * top + k; one warp per f.
 // GATED: W_up holds 2 ff rows per expert and hidden[p, f] = silu(row f . x) * (row ff + f . x).
+// limit > 0: the clamped form g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_gemv_up_kernel(const T* __restrict__ x, const int* __restrict__ ids, const T* __restrict__ w_up,
-                                                          T* __restrict__ hidden, int top, int d, int ff) {
+                                                          T* __restrict__ hidden, int top, int d, int ff, float limit, float alpha) {
   griddep_launch();
   griddep_wait();
   const int p = blockIdx.y, lane = threadIdx.x & 31;
@@ -239,8 +248,14 @@ __global__ void __launch_bounds__(256) moe_gemv_up_kernel(const T* __restrict__ 
       T gr, ur;
       store_from_float(&gr, 0, gate);
       store_from_float(&ur, 0, up);
-      const float gz = load_as_float(&gr, 0);
-      store_from_float(hidden, (int64_t)p * ff + f, gz / (1.0f + expf(-gz)) * load_as_float(&ur, 0));
+      float gz = load_as_float(&gr, 0), uz = load_as_float(&ur, 0);
+      if (limit > 0.f) {
+        gz = fminf(gz, limit);
+        uz = fminf(fmaxf(uz, -limit), limit);
+        store_from_float(hidden, (int64_t)p * ff + f, gz / (1.0f + expf(-alpha * gz)) * (uz + 1.0f));
+      } else {
+        store_from_float(hidden, (int64_t)p * ff + f, gz / (1.0f + expf(-gz)) * uz);
+      }
     }
     return;
   }
@@ -350,17 +365,19 @@ int b200_moe_gemm(const void* a, int64_t lda, const int32_t* row_src, const void
 }
 
 int b200_moe_gemv(const void* x, const int32_t* ids, const float* weights, const void* w_up, const void* w_down, void* hidden, void* out,
-                  int64_t tokens, int top, int d, int ff, int gated, int dtype, b200_stream_t stream) {
+                  int64_t tokens, int top, int d, int ff, int gated, float limit, float alpha, int dtype, b200_stream_t stream) {
   B200_CHECK_ARG(x && ids && weights && w_up && w_down && hidden && out, "b200_moe_gemv: null pointer");
+  B200_CHECK_ARG(gated >= 0 && gated <= 2 && (gated != 2 || limit > 0.f), "b200_moe_gemv: gated is 0 (relu^2), 1 (silu gate) or 2 (clamped gate, limit > 0)");
+  if (gated != 2) limit = 0.f;
   B200_CHECK_ARG(tokens > 0 && tokens * top <= 65535 && d > 0 && ff > 0, "b200_moe_gemv: bad shape");
   cudaStream_t st = (cudaStream_t)stream;
   B200_FLOAT_TYPES(dtype, T, {
     if (gated)
       B200_CUDA(launch(moe_gemv_up_kernel<T, true>, dim3((unsigned)((ff + 7) / 8), (unsigned)(tokens * top)), dim3(256), 0, st, (const T*)x, ids,
-                       (const T*)w_up, (T*)hidden, top, d, ff));
+                       (const T*)w_up, (T*)hidden, top, d, ff, limit, alpha));
     else
       B200_CUDA(launch(moe_gemv_up_kernel<T, false>, dim3((unsigned)((ff + 7) / 8), (unsigned)(tokens * top)), dim3(256), 0, st, (const T*)x, ids,
-                       (const T*)w_up, (T*)hidden, top, d, ff));
+                       (const T*)w_up, (T*)hidden, top, d, ff, limit, alpha));
     B200_CUDA(launch(moe_gemv_down_kernel<T>, dim3((unsigned)((d + 7) / 8), (unsigned)tokens), dim3(256), 0, st, (const T*)hidden, ids, weights,
                      (const T*)w_down, (T*)out, top, d, ff));
   });

@@ -313,6 +313,152 @@ __global__ void __launch_bounds__(256) glu_kernel(const T* __restrict__ in, T* _
   }
 }
 
+// xIELU in place, with the two raw parameters (p, q) read from `params`:
+//   z > 0: softplus(p) z^2 + z / 2;   z <= 0: (1 / 2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+template <typename T>
+__global__ void __launch_bounds__(256) xielu_kernel(T* __restrict__ x, int64_t n, const T* __restrict__ params) {
+  griddep_launch();
+  griddep_wait();
+  const float ap = log1pf(expf(load_as_float(params, 0))), aq = 0.5f + log1pf(expf(load_as_float(params, 1)));
+  auto f = [&](float z) { return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z); };
+  if (vec8_ok(n, x)) {
+    for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8; i < n; i += (int64_t)gridDim.x * 2048) {
+      float v[8];
+      load8(x + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = f(v[j]);
+      store8(x + i, v);
+    }
+    return;
+  }
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) store_from_float(x, i, f(load_as_float(x, i)));
+}
+
+// out[r, c] = g sigmoid(alpha g) (u + 1) with g = min(in[r, c], limit), u = clamp(in[r, ff + c], -limit, limit): the middle step of a
+// gated feed-forward with clamped branches over a fused [gate | up] product
+template <typename T>
+__global__ void __launch_bounds__(256) glu_clamped_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int ff, float limit, float alpha) {
+  griddep_launch();
+  griddep_wait();
+  auto f = [&](float g, float u) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  };
+  if (vec8_ok(ff, in, out)) {
+    const int64_t n8 = rows * (ff / 8);
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n8; i += (int64_t)gridDim.x * 256) {
+      const int64_t r = i / (ff / 8), c = (i - r * (ff / 8)) * 8;
+      float g[8], u[8];
+      load8(in + r * 2 * ff + c, g);
+      load8(in + r * 2 * ff + ff + c, u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = f(g[j], u[j]);
+      store8(out + r * ff + c, g);
+    }
+    return;
+  }
+  const int64_t n = rows * ff;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const int64_t r = i / ff, c = i - r * ff;
+    store_from_float(out, i, f(load_as_float(in, r * 2 * ff + c), load_as_float(in, r * 2 * ff + ff + c)));
+  }
+}
+
+// Residual update of a block whose sublayers read one norm and are scaled per channel, fused with the norm that feeds the next
+// block -- a dynamic tanh, which needs no statistics, so the kernel is elementwise:
+//   x   += y0 * s0 + (y1 + y2) * s1 + extra + row_add      (fp32 stream; every term optional, a missing scale is 1)
+//   cast = T(x)                                            (optional copy in the matrix-product dtype)
+//   act  = T(tanh(alpha * x) * nw + nb)                    (skipped without nw)
+struct ScaledResidualArgs {
+  const void* y0; const void* s0; const void* y1; const void* y2; const void* s1;
+  const float* extra; const void* row_add;
+  float* x; void* cast;
+  const void* alpha; const void* nw; const void* nb; void* act;
+  int64_t rows;
+  int d;
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256) scaled_residual_kernel(ScaledResidualArgs A) {
+  griddep_launch();
+  griddep_wait();
+  const int d = A.d, per = d / V;
+  const int64_t n = A.rows * per;
+  const T* y0 = reinterpret_cast<const T*>(A.y0);
+  const T* y1 = reinterpret_cast<const T*>(A.y1);
+  const T* y2 = reinterpret_cast<const T*>(A.y2);
+  const T* s0 = reinterpret_cast<const T*>(A.s0);
+  const T* s1 = reinterpret_cast<const T*>(A.s1);
+  const T* ra = reinterpret_cast<const T*>(A.row_add);
+  const T* nw = reinterpret_cast<const T*>(A.nw);
+  const T* nb = reinterpret_cast<const T*>(A.nb);
+  const bool changes = y0 || y1 || y2 || A.extra || ra;
+  const float alpha = nw ? load_as_float(reinterpret_cast<const T*>(A.alpha), 0) : 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const int64_t r = i / per;
+    const int c = (int)(i - r * per) * V;
+    const int64_t o = r * d + c;
+    float x[V], t[V], u[V], s[V];
+    if constexpr (V == 8) load8(A.x + o, x);
+    else x[0] = A.x[o];
+    if (y0) {
+      if constexpr (V == 8) { load8(y0 + o, t); if (s0) load8(s0 + c, s); }
+      else { t[0] = load_as_float(y0, o); if (s0) s[0] = load_as_float(s0, c); }
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[j] = s0 ? fmaf(t[j], s[j], x[j]) : x[j] + t[j];
+    }
+    if (y1 || y2) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) t[j] = 0.f;
+      if (y1) {
+        if constexpr (V == 8) load8(y1 + o, t);
+        else t[0] = load_as_float(y1, o);
+      }
+      if (y2) {
+        if constexpr (V == 8) load8(y2 + o, u);
+        else u[0] = load_as_float(y2, o);
+#pragma unroll
+        for (int j = 0; j < V; ++j) t[j] += u[j];
+      }
+      if (s1) {
+        if constexpr (V == 8) load8(s1 + c, s);
+        else s[0] = load_as_float(s1, c);
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[j] = s1 ? fmaf(t[j], s[j], x[j]) : x[j] + t[j];
+    }
+    if (A.extra) {
+      if constexpr (V == 8) load8(A.extra + o, t);
+      else t[0] = A.extra[o];
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[j] += t[j];
+    }
+    if (ra) {
+      if constexpr (V == 8) load8(ra + c, t);
+      else t[0] = load_as_float(ra, c);
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[j] += t[j];
+    }
+    if (changes) {
+      if constexpr (V == 8) store8(A.x + o, x);
+      else A.x[o] = x[0];
+    }
+    if (A.cast) {
+      if constexpr (V == 8) store8(reinterpret_cast<T*>(A.cast) + o, x);
+      else store_from_float(reinterpret_cast<T*>(A.cast), o, x[0]);
+    }
+    if (nw) {
+      if constexpr (V == 8) { load8(nw + c, t); load8(nb + c, u); }
+      else { t[0] = load_as_float(nw, c); u[0] = load_as_float(nb, c); }
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[j] = fmaf(tanhf(alpha * x[j]), t[j], u[j]);
+      if constexpr (V == 8) store8(reinterpret_cast<T*>(A.act) + o, x);
+      else store_from_float(reinterpret_cast<T*>(A.act), o, x[0]);
+    }
+  }
+}
+
 template <typename T, typename I>
 __global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(const T* __restrict__ src, const I* __restrict__ rows,
                                                                    T* __restrict__ dst, int d) {
@@ -463,6 +609,42 @@ int b200_glu(const void* in, void* out, int64_t rows, int ff, int kind, int dtyp
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
   B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(glu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)in, (T*)out, rows, ff, kind)));
+  return B200_OK;
+}
+
+int b200_xielu(void* x, int64_t n, const void* params, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(x && params && n > 0, "b200_xielu: bad argument");
+  int64_t blocks = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(xielu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (T*)x, n, (const T*)params)));
+  return B200_OK;
+}
+
+int b200_glu_clamped(const void* in, void* out, int64_t rows, int ff, float limit, float alpha, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(in && out && rows > 0 && ff > 0 && limit > 0.f, "b200_glu_clamped: bad argument");
+  int64_t blocks = (rows * ff + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(glu_clamped_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)in, (T*)out,
+                                               rows, ff, limit, alpha)));
+  return B200_OK;
+}
+
+int b200_scaled_residual(const b200_scaled_residual_args* a, b200_stream_t stream) {
+  B200_CHECK_ARG(a && a->x && a->rows > 0 && a->rows <= 0x7fffffff && a->d > 0, "b200_scaled_residual: bad argument");
+  B200_CHECK_ARG(!a->nw || (a->alpha && a->nb && a->act), "b200_scaled_residual: the norm needs its scalar, its offset and somewhere to go");
+  const ScaledResidualArgs A{a->y0, a->s0, a->y1, a->y2, a->s1, a->extra, a->row_add, a->x, a->cast, a->alpha, a->nw, a->nb, a->act, a->rows, a->d};
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = a->d % 8 == 0 && al(a->y0) && al(a->s0) && al(a->y1) && al(a->y2) && al(a->s1) && al(a->extra) && al(a->row_add) && al(a->x) &&
+                   al(a->cast) && al(a->nw) && al(a->nb) && al(a->act);
+  int64_t blocks = (a->rows * (vec ? a->d / 8 : a->d) + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(a->dtype, T, {
+    if (vec) B200_CUDA(launch(scaled_residual_kernel<T, 8>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, A));
+    else B200_CUDA(launch(scaled_residual_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, A));
+  });
   return B200_OK;
 }
 

@@ -2,6 +2,8 @@
 //
 //   row at position i sees positions j with 0 <= i - j < window;  p_j = exp(s_j) / (exp(sink_h) + sum_j' exp(s_j')),
 //   s_j = (q . k_j) * scale.  The sink is one learned logit per head with no key and no value: it only takes probability.
+//   Optional: a distance bias, s_j -= r1_h * ln(1 + r2_h * (i - j)) with two numbers per head, and a sigmoid output gate read from
+//   raw projections of the row (one per head, or one per output number).
 //
 // Grouped heads (query head h reads key-value head h / (H / G)), separate query-key (dk) and value (dv) sizes, any sizes,
 // operands bf16 or fp32, all arithmetic fp32 with a running maximum.
@@ -39,7 +41,19 @@ struct WaArgs {
   int ring, n_head, n_kv_head, dk, dv, window;
   float scale_log2;
   int store_ring;
+  const void* r1; const void* r2;   // distance bias per head (NULL: none)
+  const void* gate;                 // raw gate projections, rows ldg apart (NULL: none)
+  int64_t ldg;
+  int gate_mode;                    // 1: column h of the gate row; 2: column h * dv + c
 };
+
+// output gate of one number: sigmoid of the raw projection
+template <typename T>
+__device__ __forceinline__ float wa_gate(const WaArgs& A, int64_t row, int h, int c) {
+  if (!A.gate) return 1.0f;
+  const float z = load_as_float(reinterpret_cast<const T*>(A.gate), row * A.ldg + (A.gate_mode == 1 ? h : (int64_t)h * A.dv + c));
+  return 1.0f / (1.0f + expf(-z));
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kWaThreads) window_attn_kernel(WaArgs A) {
@@ -87,6 +101,10 @@ __global__ void __launch_bounds__(kWaThreads) window_attn_kernel(WaArgs A) {
   int lim[4];                                                   // position of each of this thread's rows (-1: no row)
 #pragma unroll
   for (int a = 0; a < 4; ++a) lim[a] = (r0 + ty + 16 * a < qlen) ? pos0 + r0 + ty + 16 * a : -1;
+  // scores live in the log2 domain: r1 ln(1 + r2 dist) log2(e) = r1 log2(1 + r2 dist)
+  const bool biased = A.r1 != nullptr;
+  const float r1h = biased ? load_as_float(reinterpret_cast<const T*>(A.r1), h) : 0.f;
+  const float r2h = biased ? load_as_float(reinterpret_cast<const T*>(A.r2), h) : 0.f;
 
   for (int j0 = key_lo; j0 < key_hi; j0 += kWaBN) {
     __syncthreads();
@@ -139,6 +157,7 @@ __global__ void __launch_bounds__(kWaThreads) window_attn_kernel(WaArgs A) {
       for (int b = 0; b < 4; ++b) {
         const int p = j0 + tx + 16 * b;
         if (p > lim[a] || p <= lim[a] - A.window) s[a][b] = -INFINITY;   // ahead of the row, or fallen out of its window
+        else if (biased) s[a][b] -= r1h * log2f(fmaf(r2h, (float)(lim[a] - p), 1.0f));
         mx = fmaxf(mx, s[a][b]);
       }
 #pragma unroll
@@ -193,7 +212,7 @@ __global__ void __launch_bounds__(kWaThreads) window_attn_kernel(WaArgs A) {
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
       const int cc = (b < 4 ? 0 : 64) + 4 * tx + (b & 3);
-      if (cc < dvc) store_from_float(orow, cc, o[a][b] * inv);
+      if (cc < dvc) store_from_float(orow, cc, o[a][b] * inv * wa_gate<T>(A, first + i, h, c0 + cc));
     }
   }
 }
@@ -230,6 +249,10 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
   for (int d = tid; d < dk; d += kWdThreads) qs[d] = load_as_float(reinterpret_cast<const T*>(A.q), (int64_t)row * A.ldq + (int64_t)h * dk + d) * A.scale_log2;
   __syncthreads();
   float mx = -INFINITY;
+  // distance bias in the log2 domain; visible position j of n lies n - 1 - j behind the row
+  const bool biased = A.r1 != nullptr;
+  const float r1h = biased ? load_as_float(reinterpret_cast<const T*>(A.r1), h) : 0.f;
+  const float r2h = biased ? load_as_float(reinterpret_cast<const T*>(A.r2), h) : 0.f;
   if (VEC) {
     const int sub = tid & 7, grp = tid >> 3;          // 32 groups of eight lanes, one key each per pass
     constexpr int KG = kWdThreads / 8, U = 4;         // four passes' loads are issued before any of them is used
@@ -287,6 +310,7 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
         a += __shfl_xor_sync(0xffffffffu, a, 2);
         a += __shfl_xor_sync(0xffffffffu, a, 1);
         if (j < n) {
+          if (biased) a -= r1h * log2f(fmaf(r2h, (float)(n - 1 - j), 1.0f));
           if (sub == 0) sc[j] = a;
           mx = fmaxf(mx, a);
         }
@@ -298,6 +322,7 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
       float acc = 0.f;
       for (int d = lane; d < dk; d += 32) acc = fmaf(qs[d], load_as_float(kp, d), acc);
       acc = warp_sum(acc);
+      if (biased) acc -= r1h * log2f(fmaf(r2h, (float)(n - 1 - j), 1.0f));
       if (lane == 0) sc[j] = acc;
       mx = fmaxf(mx, acc);
     }
@@ -351,7 +376,7 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
   for (int c = tid; c < dv; c += kWdThreads) {
     float t = 0.f;
     for (int r = 0; r < vrows; ++r) t += part[r * dv + c];
-    store_from_float(reinterpret_cast<T*>(A.out), (int64_t)row * A.ldo + (int64_t)h * dv + c, t * inv);
+    store_from_float(reinterpret_cast<T*>(A.out), (int64_t)row * A.ldo + (int64_t)h * dv + c, t * inv * wa_gate<T>(A, row, h, c));
   }
   // The row's own key and value enter the ring here: they replace position pos - ring, which no row of this step can see
   // (ring >= window), and every CTA reads the current position from the step's rows, never from the ring.
@@ -402,8 +427,11 @@ int b200_window_attn(const b200_window_attn_args* a, b200_stream_t stream) {
                  "b200_window_attn: bad head shape (query-key size up to 512)");
   B200_CHECK_ARG(a->window > 0 && a->ring >= a->window && a->k_ring && a->v_ring, "b200_window_attn: the ring must hold at least one window");
   B200_CHECK_ARG((reinterpret_cast<uintptr_t>(a->seqs) & 15) == 0, "b200_window_attn: seqs must be 16-byte aligned");
+  B200_CHECK_ARG(!a->dist_r1 == !a->dist_r2, "b200_window_attn: the distance bias needs both of its numbers per head");
+  B200_CHECK_ARG(a->gate_mode >= 0 && a->gate_mode <= 2 && (a->gate_mode == 0 || a->gate), "b200_window_attn: bad gate");
   const WaArgs A{a->q, a->k, a->v, a->out, a->ldq, a->ldk, a->ldv, a->ldo, a->k_ring, a->v_ring, a->sink, reinterpret_cast<const int4*>(a->seqs),
-                 a->ring, a->n_head, a->n_kv_head, a->dk, a->dv, a->window, a->scale * kLog2e, a->row_seq != nullptr};
+                 a->ring, a->n_head, a->n_kv_head, a->dk, a->dv, a->window, a->scale * kLog2e, a->row_seq != nullptr,
+                 a->dist_r1, a->dist_r2, a->gate_mode ? a->gate : nullptr, a->ldg, a->gate_mode};
   cudaStream_t st = (cudaStream_t)stream;
   const size_t esz = a->dtype == B200_F32 ? 4 : 2;
   auto aligned = [&](const void* p, int64_t ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * esz) % 16 == 0; };

@@ -752,16 +752,18 @@ def latent_decode_tune(force_any_size_kernel: bool = False) -> bool:
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_group: int, keep: int,
-              softmax: bool = False, group_max: bool = False):
+              softmax: bool = False, group_max: bool = False, topk_softmax: bool = False, bias: bool = False):
     """-> (ids int32 (n, top), weights fp32 (n, top)); see b200_moe_route.  softmax: scores are a softmax over all experts
-    instead of sigmoids; group_max: a group ranks by its largest score instead of the sum of its two largest."""
+    instead of sigmoids; group_max: a group ranks by its largest score instead of the sum of its two largest; topk_softmax: the
+    largest raw logits are chosen and weighted by a softmax over the chosen ones only; bias: `correction` is a bias inside the logit."""
     C.require_cuda(x, w_router, correction)
     n, d = x.shape
     E = w_router.shape[0]
     ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
     C.check(C.load_core().b200_moe_route(x.data_ptr(), w_router.data_ptr(), C.ptr(correction), ids.data_ptr(), wts.data_ptr(), n, d, E, top, n_group,
-                                         keep, (C.ROUTE_SOFTMAX if softmax else 0) | (C.ROUTE_GROUP_MAX if group_max else 0), _code(x),
+                                         keep, (C.ROUTE_SOFTMAX if softmax else 0) | (C.ROUTE_GROUP_MAX if group_max else 0)
+                                         | (C.ROUTE_TOPK_SOFTMAX if topk_softmax else 0) | (C.ROUTE_BIAS if bias else 0), _code(x),
                                          C.stream_ptr(x.device)), "moe_route")
     return ids, wts
 
@@ -769,9 +771,11 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
 MOE_GEMV_MAX_PAIRS = 64   # up to this many (token, choice) pairs the experts run as weight-streaming GEMVs
 
 
-def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, gated: bool = False) -> torch.Tensor:
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, gated: bool = False,
+                limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """out[t] = sum_k wts[t, k] * W_down[ids[t, k]] relu(W_up[ids[t, k]] x[t])^2 with stacked weights (E, ff, d) / (E, d, ff);
-    gated: W_up is (E, 2 ff, d), gate rows first, and the hidden vector is silu(gate) * up."""
+    gated: W_up is (E, 2 ff, d), gate rows first, and the hidden vector is silu(gate) * up -- or, with limit > 0, the clamped form
+    g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit)."""
     C.require_cuda(x, ids, wts, w_up, w_down)
     n, d = x.shape
     E, ff, top = w_up.shape[0], w_down.shape[2], ids.shape[1]
@@ -780,7 +784,7 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     if n * top <= MOE_GEMV_MAX_PAIRS:
         hidden = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
         C.check(lib.b200_moe_gemv(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), hidden.data_ptr(), out.data_ptr(),
-                                  n, top, d, ff, int(gated), code, st), "moe_gemv")
+                                  n, top, d, ff, (2 if limit > 0 else 1) if gated else 0, float(limit), float(alpha), code, st), "moe_gemv")
         return out
     plan = moe_plan(ids, E)
     up_rows = 2 * ff if gated else ff
@@ -788,7 +792,7 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     C.check(lib.b200_moe_gemm(x.data_ptr(), x.stride(0), plan.slot_token.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), up_rows,
                               plan.expert_off.data_ptr(), plan.tile_off.data_ptr(), n * top, E, up_rows, d, 0 if gated else 1, code, st), "moe_gemm(up)")
     if gated:
-        hidden = glu(hidden, C.ACT_SILU)
+        hidden = glu_clamped(hidden, limit, alpha) if limit > 0 else glu(hidden, C.ACT_SILU)
     y = torch.empty((n * top, d), dtype=x.dtype, device=x.device)
     C.check(lib.b200_moe_gemm(hidden.data_ptr(), ff, None, w_down.data_ptr(), y.data_ptr(), d, plan.expert_off.data_ptr(), plan.tile_off.data_ptr(),
                               n * top, E, d, ff, 0, code, st), "moe_gemm(down)")
@@ -863,6 +867,49 @@ def glu(x: torch.Tensor, kind: int) -> torch.Tensor:
     out = torch.empty(x.shape[:-1] + (ff,), dtype=x.dtype, device=x.device)
     C.check(C.load_core().b200_glu(x.data_ptr(), out.data_ptr(), x.numel() // (2 * ff), ff, kind, _code(x), C.stream_ptr(x.device)), "glu")
     return out
+
+
+def xielu_(x: torch.Tensor, params: torch.Tensor) -> torch.Tensor:
+    """In place: z > 0: softplus(p) z^2 + z / 2; z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2, with (p, q) = params."""
+    C.require_cuda(x, params)
+    if not x.is_contiguous() or params.dtype != x.dtype or params.numel() != 2 or not params.is_contiguous():
+        raise C.B200Error("xielu_: contiguous tensor, two parameters in its dtype")
+    C.check(C.load_core().b200_xielu(x.data_ptr(), x.numel(), params.data_ptr(), _code(x), C.stream_ptr(x.device)), "xielu")
+    return x
+
+
+def glu_clamped(x: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """x (rows, 2 ff) = [gate | up] -> g sigmoid(alpha g) (u + 1) (rows, ff), g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    C.require_cuda(x)
+    if not x.is_contiguous() or x.shape[-1] % 2:
+        raise C.B200Error("glu_clamped: contiguous rows of even length")
+    ff = x.shape[-1] // 2
+    out = torch.empty(x.shape[:-1] + (ff,), dtype=x.dtype, device=x.device)
+    C.check(C.load_core().b200_glu_clamped(x.data_ptr(), out.data_ptr(), x.numel() // (2 * ff), ff, float(limit), float(alpha), _code(x),
+                                           C.stream_ptr(x.device)), "glu_clamped")
+    return out
+
+
+def scaled_residual(x: torch.Tensor, *, y0: Optional[torch.Tensor] = None, s0: Optional[torch.Tensor] = None, y1: Optional[torch.Tensor] = None,
+                    y2: Optional[torch.Tensor] = None, s1: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+                    row_add: Optional[torch.Tensor] = None, cast: Optional[torch.Tensor] = None, norm: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+                    act: Optional[torch.Tensor] = None) -> None:
+    """x (fp32 (rows, d), in place) += y0 * s0 + (y1 + y2) * s1 + extra + row_add; cast = T(x); act = T(tanh(alpha x) * w + b) with
+    norm = (alpha, w, b).  y*, s* (d numbers), row_add (d numbers), cast and act share the matrix-product dtype; extra is fp32 rows."""
+    alpha, nw, nb = norm if norm is not None else (None, None, None)
+    C.require_cuda(x, y0, s0, y1, y2, s1, extra, row_add, cast, alpha, nw, nb, act)
+    if x.dtype != torch.float32 or not x.is_contiguous() or (extra is not None and (extra.dtype != torch.float32 or not extra.is_contiguous())):
+        raise C.B200Error("scaled_residual: the stream and extra must be contiguous fp32")
+    typed = [t for t in (y0, s0, y1, y2, s1, row_add, cast, alpha, nw, nb, act) if t is not None]
+    if not typed or any(t.dtype != typed[0].dtype or not t.is_contiguous() for t in typed):
+        raise C.B200Error("scaled_residual: branches, scales, norm and outputs in one dtype, contiguous")
+    if norm is not None and act is None:
+        raise C.B200Error("scaled_residual: the norm needs somewhere to go")
+    d = x.shape[-1]
+    args = C.ScaledResidualArgs(y0=C.ptr(y0), s0=C.ptr(s0), y1=C.ptr(y1), y2=C.ptr(y2), s1=C.ptr(s1), extra=C.ptr(extra), row_add=C.ptr(row_add),
+                                x=x.data_ptr(), cast=C.ptr(cast), alpha=C.ptr(alpha), nw=C.ptr(nw), nb=C.ptr(nb), act=C.ptr(act) if norm is not None else None,
+                                rows=x.numel() // d, d=d, dtype=_code(typed[0]))
+    C.check(C.load_core().b200_scaled_residual(ctypes.byref(args), C.stream_ptr(x.device)), "scaled_residual")
 
 
 def conv_group(w: torch.Tensor, out: torch.Tensor, col0: int, heads: int, dim: int, *, act: int = 0, post: int = 0, rot_dims: int = 0,
@@ -947,12 +994,21 @@ WINDOW_PREFILL_MMA = True   # tests switch it off to run whole prompts with tens
 
 def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch.Tensor, v_ring: torch.Tensor, sink: Optional[torch.Tensor],
                 seqs: torch.Tensor, row_seq: torch.Tensor, max_q_len: int, n_head: int, n_kv_head: int, dk: int, dv: int, window: int,
-                scale: float, from_start: bool = False) -> torch.Tensor:
+                scale: float, from_start: bool = False, *, dist: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                gate: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> torch.Tensor:
     """Sliding-window attention with a sink over this step's k / v rows and the rings (slots, ring, G * dk | dv) of earlier
     positions; afterwards the step's rows enter the rings.  -> (n, n_head * dv).  from_start: every sequence of the step begins
     at position 0, so nothing is read from the rings -- bf16 prompts with 64- or 128-wide heads then run on the tensor-core tiles
-    of the prefill kernel the other models use."""
-    C.require_cuda(q, k, v, k_ring, v_ring, sink, seqs, row_seq)
+    of the prefill kernel the other models use.  dist = (r1, r2), n_head numbers each: score -= r1 ln(1 + r2 (i - j)).  gate: raw
+    projections of the rows (n, n_head) with gate_per_head, else (n, n_head * dv); the output is multiplied by their sigmoid."""
+    r1, r2 = dist if dist is not None else (None, None)
+    C.require_cuda(q, k, v, k_ring, v_ring, sink, seqs, row_seq, r1, r2, gate)
+    if dist is not None and not (r1.dtype == r2.dtype == q.dtype and r1.numel() == r2.numel() == n_head and r1.is_contiguous() and r2.is_contiguous()):
+        raise C.B200Error("window_attn: the distance bias is two contiguous vectors of n_head numbers in the operands' dtype")
+    if gate is not None and (gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] != (n_head if gate_per_head else n_head * dv)):
+        raise C.B200Error("window_attn: the gate is (rows, n_head) or (rows, n_head * dv) in the operands' dtype with a unit inner stride")
+    gate_mode = 0 if gate is None else (1 if gate_per_head else 2)
+    ldg = 0 if gate is None else gate.stride(0)
     if not (q.dtype == k.dtype == v.dtype == k_ring.dtype == v_ring.dtype) or not (k_ring.is_contiguous() and v_ring.is_contiguous()):
         raise C.B200Error("window_attn: one dtype, contiguous rings")
     if q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1 or seqs.dtype != torch.int32 or not seqs.is_contiguous():
@@ -962,9 +1018,9 @@ def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch
     lib, st = C.load_core(), C.stream_ptr(q.device)
     if (from_start and max_q_len > 1 and WINDOW_PREFILL_MMA and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128)
             and not (q.stride(0) | k.stride(0) | v.stride(0)) & 7 and not (q.data_ptr() | k.data_ptr() | v.data_ptr() | seqs.data_ptr()) & 15):
-        C.check(lib.b200_attn_prefill_window(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), seqs.data_ptr(),
-                                             seqs.shape[0], max_q_len, out.data_ptr(), out.stride(0), n_head, n_kv_head, dk, float(scale), window,
-                                             C.ptr(sink), st), "attn_prefill_window")
+        C.check(lib.b200_attn_prefill_window_ex(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), seqs.data_ptr(),
+                                                seqs.shape[0], max_q_len, out.data_ptr(), out.stride(0), n_head, n_kv_head, dk, float(scale), window,
+                                                C.ptr(sink), C.ptr(r1), C.ptr(r2), C.ptr(gate), ldg, gate_mode, st), "attn_prefill_window")
         C.check(lib.b200_ring_store(k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_ring.data_ptr(), v_ring.data_ptr(), ring, n_kv_head * dk,
                                     n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
         return out
@@ -972,7 +1028,7 @@ def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch
     args = C.WindowAttnArgs(row_seq=row_seq.data_ptr(), rows=q.shape[0], q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(),
                             ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0), ldo=out.stride(0), k_ring=k_ring.data_ptr(), v_ring=v_ring.data_ptr(), sink=C.ptr(sink), seqs=seqs.data_ptr(),
                             n_seqs=seqs.shape[0], max_q_len=max_q_len, ring=ring, n_head=n_head, n_kv_head=n_kv_head, dk=dk, dv=dv, window=window,
-                            scale=float(scale), dtype=_code(q))
+                            scale=float(scale), dtype=_code(q), dist_r1=C.ptr(r1), dist_r2=C.ptr(r2), gate=C.ptr(gate), ldg=ldg, gate_mode=gate_mode)
     C.check(lib.b200_window_attn(ctypes.byref(args), st), "window_attn")
     return out
 

@@ -27,23 +27,28 @@ class RaggedBatch:
     identity_ctx: bool = False       # every sequence starts at position 0: the context rows ARE the step's rows, in order
 
 
-def state_batch(seqs: Sequence[Tuple[int, int, int]], device: torch.device, extra: Sequence[int] = ()) -> Tuple[RaggedBatch, torch.Tensor]:
+def state_batch(seqs: Sequence[Tuple[int, int, int]], device: torch.device, extra: Sequence[int] = (),
+                positions: bool = False) -> Tuple[RaggedBatch, torch.Tensor]:
     """The description of a step for models that keep a state per slot.  `seqs`: per sequence (state slot, position of its first
-    new row, number of new rows), rows packed in this order.  One host-to-device copy carries the table, the row map and
-    `extra` (e.g. the step's token ids), which comes back as the second result."""
+    new row, number of new rows), rows packed in this order.  One host-to-device copy carries the table, the row map, with
+    `positions` every row's position, and `extra` (e.g. the step's token ids), which comes back as the second result."""
     meta: List[int] = []
     row_seq: List[int] = []
+    row_pos: List[int] = []
     first = 0
     for i, (slot, start, length) in enumerate(seqs):
         meta.extend((first, length, start, slot))
         row_seq.extend([i] * length)
+        if positions:
+            row_pos.extend(range(start, start + length))
         first += length
     S = len(seqs)
-    i32 = torch.tensor(meta + row_seq + [int(v) for v in extra], dtype=torch.int32).to(device, non_blocking=True)
-    batch = RaggedBatch(row_pos=None, row_slot=None, cache_rows=None, decode=all(s[2] == 1 for s in seqs),
+    i32 = torch.tensor(meta + row_seq + row_pos + [int(v) for v in extra], dtype=torch.int32).to(device, non_blocking=True)
+    rest = 4 * S + first + len(row_pos)
+    batch = RaggedBatch(row_pos=i32[4 * S + first : rest] if positions else None, row_slot=None, cache_rows=None, decode=all(s[2] == 1 for s in seqs),
                         context_hint=max(s[1] + s[2] for s in seqs), max_q_len=max(s[2] for s in seqs),
                         seq_state=i32[: 4 * S].view(S, 4), row_seq=i32[4 * S : 4 * S + first], identity_ctx=all(s[1] == 0 for s in seqs))
-    return batch, i32[4 * S + first :]
+    return batch, i32[rest:]
 
 
 class SlotAllocator:

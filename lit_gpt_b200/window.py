@@ -9,6 +9,13 @@ What a sequence keeps between steps (``WindowState``, one slot per live sequence
 convolution's tail) and the keys and values of its last `ring` >= window positions, position p in ring row p % ring.  The
 projections are vendor matrix products; convolution, rotation, norm (one kernel), attention and the ring update are this
 library's kernels.
+
+``GatedWindowAttention`` is the same attention over the same rings (``RingState``) without convolution, norm or sink, and with
+
+    s_ij   -= r1_h ln(1 + r2_h (i - j))                      (optional distance bias, two learned numbers per head)
+    out     = W_o (concat_h(sum_j p_ij v_j) * sigmoid(W_g h))  (gate per output number, or one per head)
+
+optional biases on q, k, v and optional rotary positions on half-split pairs (``K.head_rope``).
 """
 from __future__ import annotations
 
@@ -19,7 +26,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import kernels as K
-from .config import WindowMixerSpec
+from .config import GatedWindowSpec, WindowMixerSpec
 from .ragged import RaggedBatch
 
 
@@ -87,3 +94,65 @@ class WindowAttention(nn.Module):
         y = K.window_attn(q, k, v, state.k_ring, state.v_ring, self.sink, batch.seq_state, batch.row_seq, batch.max_q_len, H, G, dk, dv,
                           s.window, s.scale, from_start=batch.identity_ctx)
         return F.linear(y, self.w_o, self.b_o)
+
+
+class RingState(nn.Module):
+    """Per slot: key / value rings (ring, kv_heads * dim | vdim) of a sequence's last `ring` positions."""
+
+    def __init__(self, slots: int, ring: int, k_cols: int, v_cols: int, device=None, dtype=None) -> None:
+        super().__init__()
+        self.ring = ring
+        self.register_buffer("k_ring", torch.zeros((slots, ring, k_cols), device=device, dtype=dtype), persistent=False)
+        self.register_buffer("v_ring", torch.zeros((slots, ring, v_cols), device=device, dtype=dtype), persistent=False)
+
+    def tensors(self):
+        return [self.k_ring, self.v_ring]
+
+
+class GatedWindowAttention(nn.Module):
+    def __init__(self, width: int, spec: GatedWindowSpec, eps: float = 0.0) -> None:
+        super().__init__()
+        self.spec, self.eps, self.width = spec, eps, width
+        H, G, dk, dv = spec.heads, spec.kv_heads, spec.dim, spec.vdim
+        self.gate_cols = 0 if spec.gate is None else (H if spec.gate == "head" else H * dv)
+        self.cols = H * dk + G * dk + G * dv + self.gate_cols
+        # fused projection: rows [0, H dk) queries, then G dk keys, G dv values, then the gate's rows
+        self.w_in = nn.Parameter(torch.empty(self.cols, width), requires_grad=False)
+        self.b_in = nn.Parameter(torch.zeros(self.cols), requires_grad=False) if spec.bias else None
+        self.r1 = nn.Parameter(torch.zeros(H), requires_grad=False) if spec.distance else None
+        self.r2 = nn.Parameter(torch.zeros(H), requires_grad=False) if spec.distance else None
+        self.w_o = nn.Parameter(torch.empty(width, H * dv), requires_grad=False)
+        self._freq_cache: dict = {}
+
+    def freq(self, device: torch.device) -> Optional[torch.Tensor]:
+        """Angular frequencies of the rotated pairs on `device` (fp32; made from the specification, so no cast of the module touches them)."""
+        rot = self.spec.rot
+        if rot is None or rot.dims == 0:
+            return None
+        t = self._freq_cache.get(device)
+        if t is None:
+            t = self._freq_cache[device] = torch.tensor(rot.frequencies(), dtype=torch.float32, device=device)
+        return t
+
+    def build_state(self, slots: int, device=None, dtype=None) -> RingState:
+        s = self.spec
+        return RingState(slots, s.window, s.kv_heads * s.dim, s.kv_heads * s.vdim, device, dtype)
+
+    def forward(self, h: torch.Tensor, batch: RaggedBatch, state: RingState) -> torch.Tensor:
+        """h (n, width) in the matrix-product dtype -> (n, width)"""
+        s, n = self.spec, h.shape[0]
+        H, G, dk, dv = s.heads, s.kv_heads, s.dim, s.vdim
+        proj = F.linear(h, self.w_in, self.b_in)
+        q, k, v = proj[:, : H * dk], proj[:, H * dk : (H + G) * dk], proj[:, (H + G) * dk : (H + G) * dk + G * dv]
+        gate = proj[:, (H + G) * dk + G * dv :] if self.gate_cols else None
+        fr = self.freq(h.device)
+        if fr is not None:
+            rot = s.rot
+            K.head_rope(n, batch.row_pos, self.eps,
+                        K.rope_seg(q, q, H, dk, freq=fr, rot_dims=rot.dims, interleaved=rot.interleaved, mag=rot.magnitude),
+                        K.rope_seg(k, k, G, dk, freq=fr, rot_dims=rot.dims, interleaved=rot.interleaved, mag=rot.magnitude),
+                        dtype=h.dtype, device=h.device)
+        y = K.window_attn(q, k, v, state.k_ring, state.v_ring, None, batch.seq_state, batch.row_seq, batch.max_q_len, H, G, dk, dv, s.window,
+                          s.scale, from_start=batch.identity_ctx, dist=(self.r1, self.r2) if s.distance else None, gate=gate,
+                          gate_per_head=s.gate == "head")
+        return F.linear(y, self.w_o)
