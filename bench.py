@@ -781,6 +781,171 @@ def run_lefalix_compare(args) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------------
+# --compare nulezen: the Nulezen design beside the closest existing model (Lefalix: the other design with sliding-window attention
+# over key / value rings, gated experts and an fp32 residual stream) at equal width, heads, head size, window, layers and expert
+# sizes; random weights.
+# ---------------------------------------------------------------------------------------------------------
+def run_nulezen_compare(args) -> None:
+    from lit_gpt_b200 import kernels as K
+    from lit_gpt_b200.config import (ClampedMoESpec, DeltaMixerSpec, DenseMLPSpec, GatedMoESpec, GatedWindowSpec, LefalixConfig, LefalixLayerSpec,
+                                     NulezenConfig, NulezenLayerSpec, ParallelMixerSpec, RotarySpec, WindowMixerSpec)
+    from lit_gpt_b200.lefalix import Lefalix
+    from lit_gpt_b200.nulezen import Nulezen
+    from lit_gpt_b200.ragged import state_batch
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_source = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    vocab, T = 32000, args.prompt
+    iters = max(3, min(args.steps, 20))
+    launches0 = K.launch_count()
+    bf = torch.bfloat16
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else LEFALIX_SIZES):
+        d, H, G, hs, W, rank, E, top, ff, dff = LEFALIX_SIZES[name]
+
+        def first(mlp):
+            return NulezenLayerSpec("attention", GatedWindowSpec(H, G, hs, hs, W, hs ** -0.5, distance=True, gate="element"), mlp)
+
+        def second(mlp):
+            return NulezenLayerSpec("attention_2", GatedWindowSpec(H, G, hs, hs, W, hs ** -0.5, rot=RotarySpec(dims=hs, base=1e6, interleaved=False),
+                                                                   bias=True, gate="head"), mlp)
+
+        def experts():
+            return ClampedMoESpec(E, top, ff, 7.0, shared_ff=ff, shared_limit=7.0)
+
+        nul = Nulezen(NulezenConfig(vocab_size=vocab, n_embd=d, embedding_scale=1.0, logit_scale=1.0, loop_start=0, loop_stop=2, loop_times=2,
+                                    layers=[first(DenseMLPSpec(dff)), second(experts())])).to(dev).to(bf).eval()   # two layers run twice: four layer runs
+        nul.reset_parameters()
+        nul.max_seq_length = T + 64
+        rot = RotarySpec(dims=hs // 2, base=1e6, factor=4.0, original=4096.0, fast=32.0, slow=1.0)
+
+        def par(mlp):
+            return LefalixLayerSpec("parallel", ParallelMixerSpec(WindowMixerSpec(H, G, hs, hs, 4, W, hs ** -0.5, rot), DeltaMixerSpec(H // 2, H // 4, hs, hs, 4)), mlp)
+
+        lef = Lefalix(LefalixConfig(vocab_size=vocab, n_embd=d, layers=[par(DenseMLPSpec(dff)), par(GatedMoESpec(E, top, ff, 4, 2)),
+                                                                        par(DenseMLPSpec(dff)), par(GatedMoESpec(E, top, ff, 4, 2))])).to(dev).to(bf).eval()
+        lef.reset_parameters()
+        lef.max_seq_length = T + 64
+        res = {}
+        with torch.inference_mode():
+            for label, model in (("nulezen", nul), ("lefalix", lef)):
+                for B in (1, 8):
+                    model.set_kv_cache(batch_size=B)
+                    idx = torch.randint(0, vocab, (B, T), device=dev)
+                    pos = torch.arange(T, device=dev)
+                    if B == 1:
+                        ms = _timed(lambda: model(idx, pos), iters, flush)
+                        res[f"{label}_prefill_tok_s"] = round(T / ms * 1e3)
+                    else:
+                        model(idx, pos)
+                    tok, p1 = idx[:, :1].contiguous(), torch.tensor([T], device=dev)
+                    step, graphed = _graphed(lambda: model(tok, p1))
+                    ms = _timed(step, iters, flush)
+                    res[f"{label}_decode_b{B}_tok_s"] = round(B / ms * 1e3)
+                    res[f"{label}_decode_b{B}_graphed"] = graphed
+                    del step
+                model.clear_kv_cache()
+            kern = {}
+            # prefill attention: both designs on the same tensor-core tiles; the window's work is T * W - W^2 / 2 score pairs
+            q = torch.randn(T, H * hs, device=dev, dtype=bf)
+            kv = torch.randn(T, 2 * G * hs, device=dev, dtype=bf)
+            sink = torch.zeros(H, device=dev, dtype=bf)
+            r1, r2 = torch.full((H,), 0.5, device=dev, dtype=bf), torch.ones(H, device=dev, dtype=bf)
+            gate_e, gate_h = torch.randn(T, H * hs, device=dev, dtype=bf), torch.randn(T, H, device=dev, dtype=bf)
+            batch, _ = state_batch([(0, 0, T)], dev, positions=True)
+            kr, vr = torch.zeros(1, W, G * hs, device=dev, dtype=bf), torch.zeros(1, W, G * hs, device=dev, dtype=bf)
+            pairs = sum(min(i + 1, W) for i in range(T))
+            kk, vv = kv[:, : G * hs], kv[:, G * hs :]
+
+            def win(qq, k_, v_, b, rows, **kw):
+                return K.window_attn(qq, k_, v_, kr if rows > 1 else krb, vr if rows > 1 else vrb, kw.pop("sink", None), b.seq_state, b.row_seq, rows, H, G,
+                                     hs, hs, W, hs ** -0.5, from_start=rows > 1, **kw)
+
+            for label, kw in (("nulezen_distance_bias_gate_per_number", dict(dist=(r1, r2), gate=gate_e)),
+                              ("nulezen_gate_per_head", dict(gate=gate_h, gate_per_head=True)), ("lefalix_sink", dict(sink=sink))):
+                ms = _timed(lambda: win(q, kk, vv, batch, T, **dict(kw)), iters, flush)
+                kern[f"prefill_attention_{label}"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * H * hs * pairs / (ms * 1e-3) / tf, "includes": "ring store"}
+            # decode attention: bytes that must come from HBM
+            B = 8
+            qd, kd = torch.randn(B, H * hs, device=dev, dtype=bf), torch.randn(B, 2 * G * hs, device=dev, dtype=bf)
+            krb, vrb = torch.randn(B, W, G * hs, device=dev, dtype=bf), torch.randn(B, W, G * hs, device=dev, dtype=bf)
+            bd, _ = state_batch([(b, T, 1) for b in range(B)], dev, positions=True)
+            roof = 2.0 * B * G * W * hs * 2 / hbm
+            for label, kw in (("nulezen_distance_bias_gate_per_number", dict(dist=(r1, r2), gate=gate_e[:B])),
+                              ("nulezen_gate_per_head", dict(gate=gate_h[:B], gate_per_head=True)), ("lefalix_sink", dict(sink=sink))):
+                ms = _timed(lambda: win(qd, kd[:, : G * hs], kd[:, G * hs :], bd, 1, **dict(kw)), iters, flush)
+                kern[f"decode_attention_{label}"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": 2.0 * B * G * W * hs * 2,
+                                                     "includes": "ring store"}
+            # rotation of q and k in place beside Lefalix's convolution + rotation + norm (both read and write each projected number once)
+            nm = nul.blocks[1].mixer
+            proj = torch.randn(T, nm.cols, device=dev, dtype=bf)
+            fr = nm.freq(dev)
+            qv, kv_ = proj[:, : H * hs], proj[:, H * hs : (H + G) * hs]
+            ms = _timed(lambda: K.head_rope(T, batch.row_pos, 0.0, K.rope_seg(qv, qv, H, hs, freq=fr, rot_dims=hs, interleaved=False),
+                                            K.rope_seg(kv_, kv_, G, hs, freq=fr, rot_dims=hs, interleaved=False), dtype=bf, device=dev), iters, flush)
+            kern["rotation_nulezen"] = {"ms": ms, "frac_of_measured_hbm": T * (H + G) * hs * 4.0 / (ms * 1e-3) / hbm}
+            wm = lef.blocks[1].mixer.left
+            cols = wm.cols
+            qkv, dst = torch.randn(T, cols, device=dev, dtype=bf), torch.empty(T, cols, device=dev, dtype=bf)
+            tail = torch.zeros(1, 3, cols, device=dev, dtype=bf)
+            fl = wm.inv_freq(dev)
+            groups = [K.conv_group(wm.conv[: H * hs], dst[:, : H * hs], 0, H, hs, post=1, rot_dims=hs // 2, inv_freq=fl, rot_mscale=rot.magnitude, eps=1e-5),
+                      K.conv_group(wm.conv[H * hs : (H + G) * hs], dst[:, H * hs : (H + G) * hs], H * hs, G, hs, post=1, rot_dims=hs // 2, inv_freq=fl,
+                                   rot_mscale=rot.magnitude, eps=1e-5),
+                      K.conv_group(wm.conv[(H + G) * hs :], dst[:, (H + G) * hs :], (H + G) * hs, G, hs)]
+            ms = _timed(lambda: K.short_conv(qkv, groups, 4, tail, batch.seq_state, batch.row_seq), iters, flush)
+            kern["short_conv_rotate_norm_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * cols * 4.0 / (ms * 1e-3) / hbm}
+            # residual kernels
+            x, x2, x3 = (torch.randn(T, d, device=dev, dtype=bf) for _ in range(3))
+            xs, act = torch.randn(T, d, device=dev), torch.empty(T, d, device=dev, dtype=bf)
+            nb_, lb = nul.blocks[1], lef.blocks[1]
+            ms = _timed(lambda: K.scaled_residual(xs, y0=x, s0=nb_.ls1, y1=x2, y2=x3, s1=nb_.ls2, norm=nb_.norm.terms(), act=act), iters, flush)
+            kern["residual_three_branches_norm_nulezen"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 2 + 2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.scaled_residual(xs, y0=x, s0=nb_.ls1, y1=x2, s1=nb_.ls2, norm=nb_.norm.terms(), act=act), iters, flush)
+            kern["residual_two_branches_norm_nulezen"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.sandwich_residual(xs, x, lb.norm_1b, 1e-5, w0=lb.mixer.left_out, y1=x2, w1=lb.mixer.right_out, pre_w=lb.norm_2, act=act),
+                        iters, flush)
+            kern["residual_two_branches_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            # feed-forwards over T tokens
+            ms = _timed(lambda: nb_.mlp(x), iters, flush)
+            kern["experts_nulezen"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: lb.mlp(x), iters, flush)
+            kern["experts_lefalix"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: nb_.mlp.shared(x), iters, flush)
+            kern["shared_expert_nulezen"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * ff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: nul.blocks[0].mlp(x), iters, flush)
+            kern["dense_mlp_xielu_nulezen"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * dff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: lef.blocks[0].mlp(x), iters, flush)
+            kern["dense_mlp_gelu_lefalix"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * dff * d / (ms * 1e-3) / tf}
+            # the activations alone (bytes read and written once)
+            hid, both = torch.randn(T, dff, device=dev, dtype=bf), torch.randn(T * top, 2 * ff, device=dev, dtype=bf)
+            ms = _timed(lambda: K.xielu_(hid, nul.blocks[0].mlp.act), iters, flush)
+            kern["xielu_nulezen"] = {"ms": ms, "frac_of_measured_hbm": T * dff * 4.0 / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.activation_(hid, K.ACT_GELU), iters, flush)
+            kern["gelu_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * dff * 4.0 / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.glu_clamped(both, 7.0, 1.702), iters, flush)
+            kern["clamped_gate_nulezen"] = {"ms": ms, "frac_of_measured_hbm": T * top * ff * 6.0 / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.glu(both, K.ACT_SILU), iters, flush)
+            kern["silu_gate_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * top * ff * 6.0 / (ms * 1e-3) / hbm}
+            # routers (one CTA per token; reads the token and the router's rows)
+            ms = _timed(lambda: nb_.mlp.router(x), iters, flush)
+            kern["router_nulezen"] = {"ms": ms, "us_per_token": ms * 1e3 / T}
+            ms = _timed(lambda: lb.mlp.router(x), iters, flush)
+            kern["router_lefalix"] = {"ms": ms, "us_per_token": ms * 1e3 / T}
+            res["kernels"] = {k: {a: (round(b, 4) if isinstance(b, float) else b) for a, b in v.items()} for k, v in kern.items()}
+        out[name] = res
+        del nul, lef
+        torch.cuda.empty_cache()
+    print(json.dumps({"compare": "nulezen", "layers": 4, "prompt": T, "context": T, "dtype": "bf16", "data": "synthetic, random weights",
+                      "l2": "flushed between timed calls", "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                                                                       "source": peak_source},
+                      "gpu_launches": int(K.launch_count() - launches0), "sizes": out}), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
 # --compare fizadra: the Fizadra design beside the closest existing model (Pomipel: the other design with latent attention over an
 # fp32 residual stream) at equal width, heads, head size, latent size and layers; random weights.
 # ---------------------------------------------------------------------------------------------------------
@@ -947,11 +1112,14 @@ def main() -> None:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama2-7b-nf4-bs1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: build fewer blocks (invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--compare", choices=["pomipel", "lefalix", "fizadra"], default=None,
+    ap.add_argument("--compare", choices=["pomipel", "lefalix", "fizadra", "nulezen"], default=None,
                     help="instead of the default workload: prefill / decode throughput of that design beside the closest existing model")
     ap.add_argument("--sizes", default=None, help=f"--compare: comma-separated subset of {sorted(ARCH_SIZES)} (the same names for both designs)")
     ap.add_argument("--prompt", type=int, default=2048, help="--compare: prompt and context length")
     args = ap.parse_args()
+    if args.compare == "nulezen":
+        run_nulezen_compare(args)
+        return
     if args.compare == "fizadra":
         run_fizadra_compare(args)
         return
