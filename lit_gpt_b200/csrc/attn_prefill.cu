@@ -54,10 +54,14 @@ struct PfView {
   int64_t s_h;
   int s_qt, s_kt;
   int64_t kv_slot_rows;
-  // ragged only: a distance bias, score -= dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (both NULL: none)
+  // ragged only: a distance bias, score -= dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (both NULL: none).  bias_n > 0: the CTA tabulates
+  // the bias of the distances [0, bias_n) in shared memory behind its tiles (bias_n covers every visible distance); 0: computed in place.
   const __nv_bfloat16* dist_r1;
   const __nv_bfloat16* dist_r2;
+  int bias_n;
 };
+
+constexpr int kPfBiasTabMax = 8192;   // distances a CTA tabulates at most (32 KB)
 
 template <int HS, typename PosT, int HK2 = 0, int MODE = 0>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -73,6 +77,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   constexpr int CH2 = HK2 / 8, KB2 = kPfBN * HK2 * 2;
   uint8_t* const sQ2 = sV + 2 * KB;                  // [128][HK2]  the query columns that meet the shared key part
   uint8_t* const sK2 = sQ2 + kPfBM * HK2 * 2;        // [2][64][HK2]
+  float* const sTab = reinterpret_cast<float*>(sK2 + 2 * KB2);   // [bias_n] distance bias by distance, in units of the raw dot product
   __shared__ int s_maxpos[kPfThreads / 32];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
@@ -163,6 +168,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   for (int i = 0; i < HS / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
   float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
 
+  // distance bias on the raw dot products: (s - r1 log2(1 + r2 dist) / scale_log2) * scale_log2 is the biased score in the log2 domain
+  const bool biased = MODE == 0 && vw.seqs && vw.dist_r1;
+  const float r1q = biased ? __bfloat162float(vw.dist_r1[h]) / scale_log2 : 0.f, r2h = biased ? __bfloat162float(vw.dist_r2[h]) : 0.f;
+  const int ntab = biased ? vw.bias_n : 0;
+  for (int i = tid; i < ntab; i += kPfThreads) sTab[i] = r1q * log2f(fmaf(r2h, (float)i, 1.0f));
+
   // Q fragments stay in registers for the whole key loop
   pf_wait<1>();
   __syncthreads();
@@ -182,9 +193,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   const int warp_lim = wl;
-  // distance bias on the raw dot products: (s - r1 log2(1 + r2 dist) / scale_log2) * scale_log2 is the biased score in the log2 domain
-  const bool biased = MODE == 0 && vw.seqs && vw.dist_r1;
-  const float r1q = biased ? __bfloat162float(vw.dist_r1[h]) / scale_log2 : 0.f, r2h = biased ? __bfloat162float(vw.dist_r2[h]) : 0.f;
   for (int tile = tile_lo; tile < ntiles; ++tile) {
     const int buf = tile & 1;
     if (tile + 1 < ntiles) { load_kv(tile + 1, buf ^ 1); pf_wait<1>(); } else { pf_wait<0>(); }
@@ -237,15 +245,26 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const bool need_mask = j0 + kPfBN - 1 > min(limA < 0 ? 0x7fffffff : limA, limB < 0 ? 0x7fffffff : limB) || limA < 0 || limB < 0 ||
                              (window > 0 && j0 < max(loA, loB));
       float tmA = -INFINITY, tmB = -INFINITY;
-      if (biased) {   // entries ahead of the row get a meaningless bias and are masked below
+      if (biased) {
+        // The bias depends on row - key only, and this thread's second row lies 8 below its first: entry (i, c) of the first row is
+        // e - 8 (i + 1) - c away from its key, of the second e - 8 i - c, so 18 values serve the thread's 32 entries.  Entries ahead of
+        // a row (negative distance) or beyond the table get a neighbour's value and are masked below.
+        const int e = limA + 8 - j0 - 2 * tq;
+        float vb[kPfBN / 8 + 1][2];
+#pragma unroll
+        for (int m = 0; m <= kPfBN / 8; ++m) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int dd = max(e - 8 * m - c, 0);
+            vb[m][c] = ntab > 0 ? sTab[min(dd, ntab - 1)] : r1q * log2f(fmaf(r2h, (float)dd, 1.0f));
+          }
+        }
 #pragma unroll
         for (int i = 0; i < kPfBN / 8; ++i) {
-          const int j = j0 + i * 8 + 2 * tq;
-          const float dA = (float)max(limA - j, 0), dB = (float)max(limB - j, 0);
-          s[i][0] -= r1q * log2f(fmaf(r2h, dA, 1.0f));
-          s[i][1] -= r1q * log2f(fmaf(r2h, fmaxf(dA - 1.0f, 0.f), 1.0f));
-          s[i][2] -= r1q * log2f(fmaf(r2h, dB, 1.0f));
-          s[i][3] -= r1q * log2f(fmaf(r2h, fmaxf(dB - 1.0f, 0.f), 1.0f));
+          s[i][0] -= vb[i + 1][0];
+          s[i][1] -= vb[i + 1][1];
+          s[i][2] -= vb[i][0];
+          s[i][3] -= vb[i][1];
         }
       }
 #pragma unroll
@@ -307,7 +326,21 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     iB = cB / (lB * cB + exp2f(sk - eB));
   }
   const int gmode = vw.seqs && vw.gate ? vw.gate_mode : 0;
-  auto sigm = [](const __nv_bfloat16* p) -> float { return 1.0f / (1.0f + expf(-__bfloat162float(*p))); };
+  // the gate's sigmoid with the fast exponential and reciprocal: the product is rounded to bf16 right after
+  auto sigf = [](float z) -> float { return __fdividef(1.0f, 1.0f + __expf(-z)); };
+  auto sigm = [&](const __nv_bfloat16* p) -> float { return sigf(__bfloat162float(*p)); };
+  // a pair of neighbouring gates as one 4-byte load when every pair starts on a 4-byte boundary
+  const bool gate_pairs = gmode == 2 && (reinterpret_cast<uintptr_t>(vw.gate) & 3) == 0 && (vw.gate_r & 1) == 0;
+  auto gate2 = [&](const __nv_bfloat16* p, float& a0, float& a1) {
+    if (gate_pairs) {
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+      a0 *= sigf(bf16lo(v));
+      a1 *= sigf(bf16hi(v));
+    } else {
+      a0 *= sigm(p);
+      a1 *= sigm(p + 1);
+    }
+  };
   if (rowA < T) {
     __nv_bfloat16* yr = y + (int64_t)b * vw.y_b + (qrow0 + rowA) * vw.y_r + (int64_t)h * HS;
     const __nv_bfloat16* gr = gmode ? vw.gate + (qrow0 + rowA) * vw.gate_r : nullptr;
@@ -315,7 +348,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int i = 0; i < HS / 8; ++i) {
       float a0 = o_acc[i][0] * iA, a1 = o_acc[i][1] * iA;
-      if (gmode == 2) { a0 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq); a1 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq + 1); }
+      if (gmode == 2) gate2(gr + (int64_t)h * HS + i * 8 + 2 * tq, a0, a1);
       *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(a0, a1);
     }
   }
@@ -326,7 +359,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int i = 0; i < HS / 8; ++i) {
       float a0 = o_acc[i][2] * iB, a1 = o_acc[i][3] * iB;
-      if (gmode == 2) { a0 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq); a1 *= sigm(gr + (int64_t)h * HS + i * 8 + 2 * tq + 1); }
+      if (gmode == 2) gate2(gr + (int64_t)h * HS + i * 8 + 2 * tq, a0, a1);
       *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(a0, a1);
     }
   }
@@ -340,10 +373,12 @@ cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const 
                          : PfView{(int64_t)H * T * HS, (int64_t)T * HS, HS, (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS,
                                   (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr, 0, nullptr, 0,
                                   nullptr, 0, nullptr, 0, 0, nullptr, 0, 0, 0, 0};
-  const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2 + (size_t)(kPfBM + 2 * kPfBN) * HK2 * 2;
+  const size_t tiles = (size_t)(kPfBM + 4 * kPfBN) * HS * 2 + (size_t)(kPfBM + 2 * kPfBN) * HK2 * 2;
+  const size_t smem = tiles + (size_t)vw.bias_n * sizeof(float);
   static PerDeviceOnce once;
   if (once.need()) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HS, PosT, HK2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HS, PosT, HK2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(tiles + kPfBiasTabMax * sizeof(float)));
     if (e != cudaSuccess) return e;
     once.done();
   }
@@ -498,9 +533,12 @@ extern "C" int b200_attn_prefill_window_ex(const void* q, int64_t ldq, const voi
   B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0, "b200_attn_prefill_window: leading dimensions must be multiples of 8 elements");
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_window: operands must be 16-byte aligned");
+  // every visible distance is below the window (or, without one, below the longest sequence of this step, which starts at 0)
+  const int reach = window > 0 ? (window < max_q_len ? window : max_q_len) : max_q_len;
   const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), window,
                   reinterpret_cast<const __nv_bfloat16*>(sink), 1, nullptr, 0, gate_mode ? reinterpret_cast<const __nv_bfloat16*>(gate) : nullptr, ldg,
-                  gate_mode, nullptr, 0, 0, 0, 0, reinterpret_cast<const __nv_bfloat16*>(r1), reinterpret_cast<const __nv_bfloat16*>(r2)};
+                  gate_mode, nullptr, 0, 0, 0, 0, reinterpret_cast<const __nv_bfloat16*>(r1), reinterpret_cast<const __nv_bfloat16*>(r2),
+                  r1 && reach <= kPfBiasTabMax ? reach : 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));

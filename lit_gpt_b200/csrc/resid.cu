@@ -320,7 +320,12 @@ __global__ void __launch_bounds__(256) xielu_kernel(T* __restrict__ x, int64_t n
   griddep_launch();
   griddep_wait();
   const float ap = log1pf(expf(load_as_float(params, 0))), aq = 0.5f + log1pf(expf(load_as_float(params, 1)));
-  auto f = [&](float z) { return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z); };
+  // 16-bit rows take the fast exponential: its absolute error (about 2e-7) is far below the rounding of what is stored; fp32 rows
+  // take expm1, which keeps exp(z) - 1 - z accurate for small z
+  auto f = [&](float z) {
+    const float neg = sizeof(T) == 2 ? __expf(fminf(z, 0.f)) - 1.0f - z : expm1f(fminf(z, 0.f)) - z;
+    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, neg, 0.5f * z);
+  };
   if (vec8_ok(n, x)) {
     for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8; i < n; i += (int64_t)gridDim.x * 2048) {
       float v[8];
