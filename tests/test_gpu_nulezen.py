@@ -75,7 +75,7 @@ CFG_WIDE = config(width=64, vocab=120, emb=1.0, logit=1.0, layers=[
 CFG_TILES = config(width=96, vocab=140, loop=(0, 2, 2), layers=[
     layer("attention", attn(4, 2, 64, 64, size=44), moe(8, 3, 48, 1.4, shared=(64, 1.0))),
     layer("attention_2", attn2(2, 1, 128, 128, size=100, rot_dims=64, base=1e4, scale=0.2), dense(200)),
-    layer("attention_2", attn2(4, 4, 64, 64, size=70, rot_dims=64, base=5e5), None),
+    layer("attention_2", attn2(4, 4, 64, 64, size=70, rot_dims=64, base=2e5), None),
 ])
 
 
@@ -406,6 +406,32 @@ def test_gated_window_prefill_on_the_tensor_cores(hs, size, per_head):
                 assert torch.equal(k_ring[slot, p % ring].cpu(), kk[first + p]) and torch.equal(v_ring[slot, p % ring].cpu(), v[first + p])
     assert rel_err(outs[False], want) < 6e-3
     assert rel_err(outs[True], want) < 1.2e-2
+
+
+def test_distance_bias_beyond_the_tabulated_reach():
+    """A prompt and a window longer than the distances a CTA tabulates: the tensor-core tiles compute the bias in place and agree
+    with the any-size kernel."""
+    k = K()
+    from lit_gpt_b200.ragged import state_batch
+
+    H, G, hs, n, size = 2, 1, 64, 8300, 9000
+    g = torch.Generator().manual_seed(77)
+    q = torch.randn(n, H * hs, generator=g).to(torch.bfloat16).cuda()
+    kk = torch.randn(n, G * hs, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(n, G * hs, generator=g).to(torch.bfloat16).cuda()
+    r1, r2 = torch.tensor([1.5, 0.75]).to(torch.bfloat16).cuda(), torch.tensor([0.5, 4.0]).to(torch.bfloat16).cuda()
+    batch, _ = state_batch([(0, 0, n)], torch.device("cuda"))
+    outs = {}
+    for mma in (True, False):
+        k.WINDOW_PREFILL_MMA = mma
+        try:
+            k_ring, v_ring = torch.zeros(1, size, G * hs, dtype=torch.bfloat16, device="cuda"), torch.zeros(1, size, G * hs, dtype=torch.bfloat16, device="cuda")
+            outs[mma] = k.window_attn(q, kk, v, k_ring, v_ring, None, batch.seq_state, batch.row_seq, n, H, G, hs, hs, size, 3.0 * hs ** -0.5,
+                                      from_start=True, dist=(r1, r2)).float().cpu()
+        finally:
+            k.WINDOW_PREFILL_MMA = True
+    assert rel_err(outs[True], outs[False]) < 1.2e-2
+    assert rel_err(outs[True][-200:], outs[False][-200:]) < 1.2e-2     # the rows that look farthest back
 
 
 # ---------------------------------------------------------------------------------------------------------
