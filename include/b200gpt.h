@@ -443,7 +443,7 @@ int b200_latent_decode_tune(int force_any_size_kernel);
 /* Router: s = sigmoid(W_router x), or softmax over all experts with B200_ROUTE_SOFTMAX; experts are chosen by s + correction among
  * the `keep` best of `n_group` equal groups of neighbours (group rank = sum of its two largest corrected scores, or the largest
  * with B200_ROUTE_GROUP_MAX); weights[t, k] = s of the chosen expert, not renormalised.  B200_ROUTE_TOPK_SOFTMAX: s is the raw logit,
- * the largest logits are chosen and the weights are a softmax over the chosen logits only.  B200_ROUTE_BIAS: `correction` is a bias
+ * the largest logits are chosen and the weights are a softmax among those `top` logits.  B200_ROUTE_BIAS: `correction` is a bias
  * added to the logit itself (it enters the scores) instead of a selection-only term. */
 enum b200_route_flags { B200_ROUTE_SOFTMAX = 1, B200_ROUTE_GROUP_MAX = 2, B200_ROUTE_TOPK_SOFTMAX = 4, B200_ROUTE_BIAS = 8 };
 int b200_moe_route(const void* x, const void* w_router, const void* correction, int32_t* ids, float* weights, int64_t tokens, int d,

@@ -619,7 +619,7 @@ class GatedWindowSpec:
 
 @dataclass
 class ClampedMoESpec:
-    """Experts chosen by the largest biased router logits, weighted by a softmax over the chosen logits only; expert:
+    """Experts chosen by the largest biased router logits, weighted by a softmax among those `top` logits; expert:
     W_down (g sigmoid(alpha g) (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit); optionally a shared expert of
     the same form (its own ff and limit) that every token uses."""
 

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restri
     }
     __syncwarp();
   }
-  if ((flags & B200_ROUTE_TOPK_SOFTMAX) && lane == 0) {   // weights = softmax over the chosen logits only
+  if ((flags & B200_ROUTE_TOPK_SOFTMAX) && lane == 0) {   // weights = softmax among those `top` logits
     float mx = -INFINITY, sum = 0.f;
     for (int k = 0; k < top; ++k) mx = fmaxf(mx, score[ids[t * top + k]]);
     for (int k = 0; k < top; ++k) sum += expf(score[ids[t * top + k]] - mx);

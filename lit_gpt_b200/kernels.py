@@ -755,7 +755,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
               softmax: bool = False, group_max: bool = False, topk_softmax: bool = False, bias: bool = False):
     """-> (ids int32 (n, top), weights fp32 (n, top)); see b200_moe_route.  softmax: scores are a softmax over all experts
     instead of sigmoids; group_max: a group ranks by its largest score instead of the sum of its two largest; topk_softmax: the
-    largest raw logits are chosen and weighted by a softmax over the chosen ones only; bias: `correction` is a bias inside the logit."""
+    largest raw logits are chosen and weighted by a softmax among those few; bias: `correction` is a bias inside the logit."""
     C.require_cuda(x, w_router, correction)
     n, d = x.shape
     E = w_router.shape[0]

@@ -11,8 +11,8 @@ otherwise) and as weight-streaming GEMVs for a few (``K.moe_experts``).
 score; ``GatedSparseExperts`` uses it with gated experts, out = sum_k s_k * W_down[e_k] (silu(W_gate[e_k] x) * (W_up[e_k] x)), gate
 and up rows stacked into one (experts, 2 ff, width) tensor so that both are one (grouped) product.
 
-``ClampedSparseExperts``: the router adds a bias to its logits, takes the `top` largest and weights them by a softmax over the chosen
-logits only; experts are gated with clamped branches, W_down (g sigmoid(alpha g) (u + 1)), g = min(W_gate x, limit), u = clamp(W_up x,
+``ClampedSparseExperts``: the router adds a bias to its logits, takes the `top` largest and weights them by a softmax among
+those few; experts are gated with clamped branches, W_down (g sigmoid(alpha g) (u + 1)), g = min(W_gate x, limit), u = clamp(W_up x,
 -limit, limit); ``ClampedGLU`` is one such expert for every token (a shared expert).
 """
 from __future__ import annotations
@@ -30,7 +30,7 @@ VENDOR_GROUPED_GEMM = True   # tests switch it off to run the library's own grou
 class GroupLimitedRouter(nn.Module):
     def __init__(self, width: int, experts: int, top: int, groups: int = 1, keep: int = 1, *, softmax: bool = False, group_max: bool = False,
                  correction: bool = True, topk_softmax: bool = False, bias: bool = False) -> None:
-        """topk_softmax: raw logits choose, weights = softmax over the chosen ones; bias: `correction` is a bias inside the logit."""
+        """topk_softmax: raw logits choose, weights = softmax among those few; bias: `correction` is a bias inside the logit."""
         super().__init__()
         self.top, self.groups, self.keep, self.softmax, self.group_max = top, groups, keep, softmax, group_max
         self.topk_softmax, self.bias = topk_softmax, bias

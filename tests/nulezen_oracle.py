@@ -92,7 +92,7 @@ def clamped_expert(h, W, p, limit, alpha=1.702):
 
 
 def route(h, W, p, top):
-    """-> (ids (T, top), weights (T, top)): the largest biased logits, softmax over the chosen ones only"""
+    """-> (ids (T, top), weights (T, top)): the largest biased logits, softmax among those few"""
     z = h @ W[p + "router"].T + W[p + "router.b"]
     val, idx = torch.topk(z, top, dim=-1)
     return idx, torch.softmax(val, dim=-1)
