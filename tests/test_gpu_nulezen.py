@@ -251,7 +251,9 @@ def test_clamped_experts_with_shared_expert(dtype, n):
     want = O.sparse_ff(h.double(), W, "l0.mlp.", ml)
     mlp = model.blocks[0].mlp
     got = mlp(h.to(dtype).cuda()).float() + mlp.shared(h.to(dtype).cuda()).float()
-    assert_close(got, want, dtype)
+    # the module and the oracle get the same (bf16-rounded) rows, so both route alike and EVERY row must be within rounding
+    rows = (got.double().cpu() - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-30)
+    assert float(rows.max()) < (3e-5 if dtype == torch.float32 else 2e-2), rows
     if dtype == torch.bfloat16 and n > 64:   # the vendor's grouped product against this library's own grouped kernel
         M.VENDOR_GROUPED_GEMM = False
         try:
